@@ -12,6 +12,7 @@ from ..config.base import find_architecture
 from . import qwen3  # registers Qwen3ForCausalLM
 from . import sugizen  # registers Sugizen
 from . import tinuzen  # registers Tinuzen
+from . import vusalix  # registers Vusalix
 
 for _name in filter(None, (m.strip() for m in os.environ.get("ULTIMA_ARCH_MODULES", "").split(","))):
     importlib.import_module(_name)

@@ -60,7 +60,9 @@ class KVGroup:
         self.pages_of = [[] for _ in range(n_slots)]
         shape = (len(self.runs), n_pages, need.n_kv_heads, PAGE, need.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
+        # values that are columns of the key rows have no pages of their own
+        self.v = self.k if need.values_in_keys else \
+            torch.empty(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
         if poison:
             self.k.fill_(float("nan"))
             self.v.fill_(float("nan"))
@@ -73,7 +75,7 @@ class KVGroup:
         return self.ring_pages * PAGE
 
     def nbytes(self) -> int:
-        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+        return (self.k.numel() + (0 if self.v is self.k else self.v.numel())) * self.k.element_size()
 
 
 class StateGroup:

@@ -3,7 +3,8 @@ from .base import (ConfigError, ArchitectureConfig, ArchitectureEntry, register_
                    known_architectures, read_config_json, config_from_dict, config_from_dir)
 from .qwen3 import Qwen3Config
 from .sugizen import SugizenConfig
+from .vusalix import VusalixConfig
 
 __all__ = ["ConfigError", "ArchitectureConfig", "ArchitectureEntry", "register_architecture", "find_architecture",
            "known_architectures", "read_config_json", "config_from_dict", "config_from_dir",
-           "Qwen3Config", "SugizenConfig"]
+           "Qwen3Config", "SugizenConfig", "VusalixConfig"]

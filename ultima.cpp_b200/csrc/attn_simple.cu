@@ -14,7 +14,12 @@
 // multiplies the output by its sigmoid.  Further options, all off at zero: ``keep_first`` > 0 with a
 // window: the sequence's first keep_first positions stay visible behind the window; ``slopes`` (float32,
 // one a head): slope * (distance to the key) is taken off a score; ``sink``: the softmax's sum has one
-// more term exp(0) that brings no value; ``out_scale`` multiplies the output.  The
+// more term exp(0) that brings no value (``sink_vals``, float32, one a head: the term is exp(sink_vals[h])
+// instead); ``softcap`` > 0: a scaled score s becomes softcap * tanh(s / softcap); ``dist_bias`` (float32
+// [n_dist, heads]): row min(distance to the key, n_dist - 1) is added to the score behind scale and cap (a
+// learned bias by distance, looked up per head); ``out_scale`` multiplies the output.  Key rows may be up
+// to 1,024 wide and value rows up to 512; the values may be the leading columns of the key rows (the caller
+// then hands the key cache in twice, with the keys' head size as the values' row size ``v_row``).  The
 // placement kernels at the end prepare queries and fill the cache from projection rows whose q, k and
 // v columns lie anywhere, for layers the fused preparation of basic.cu does not take (unequal head
 // sizes, no keys and values of their own, a norm over all heads at once, values that are the keys).
@@ -28,13 +33,15 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
                    const TC* __restrict__ vc, TQ* __restrict__ out, long long o_stride,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, PagedKV c, PagedKV cv,
                    int nh, int window, int block, const float* __restrict__ gate, long long g_stride, float scale,
-                   int keep_first, const float* __restrict__ slopes, int sink, int gate_wide, float out_scale) {
+                   int keep_first, const float* __restrict__ slopes, int sink, int gate_wide, float out_scale,
+                   float softcap, const float* __restrict__ dist_bias, int n_dist, const float* __restrict__ sink_vals,
+                   int hdv) {
     extern __shared__ float smem[];
     float* qs = smem;                    // [hd]
     float* sc = smem + c.head_dim;       // [CHUNK]
     __shared__ float red[33];
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    const int hd = c.head_dim, hdv = cv.head_dim;
+    const int hd = c.head_dim;
     const int kvh = h / (nh / c.n_kv_heads);
     const int pos = tok_pos[t], seq = tok_seq[t];
     int lo = 0;
@@ -43,7 +50,9 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
     for (int i = tid; i < hd; i += blockDim.x) qs[i] = to_f32<TQ>(q[(long long)t * q_stride + (long long)h * hd + i]);
     __syncthreads();
     // the sink is a key with score 0 and no value: the running maximum and sum start from it
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f, acc0 = 0.f, acc1 = 0.f;
+    float m = sink ? (sink_vals ? sink_vals[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
     // visible keys: the kept first positions that the window has left behind, then lo .. pos
     const int n_kept = min(max(keep_first, 0), lo);
     const int n_keys = n_kept + pos + 1 - lo;
@@ -56,7 +65,10 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
             const TC* kr = kc + paged_offset(c, seq, key, kvh);
             float s = 0.f;
             for (int i = 0; i < hd; ++i) s = fmaf(qs[i], to_f32<TC>(kr[i]), s);
-            s = s * scale - slope * (float)(pos - key);
+            s = s * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+            s -= slope * (float)(pos - key);
+            if (dist_bias) s += dist_bias[(long long)min(pos - key, n_dist - 1) * nh + h];
             sc[j] = s;
             cmax = fmaxf(cmax, s);
         }
@@ -72,14 +84,15 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
         psum = block_sum(psum, red);                 // also orders the writes of sc before the reads
         l = l * corr + psum;
         m = m_new;
-        acc0 *= corr;
-        acc1 *= corr;
+#pragma unroll
+        for (int a = 0; a < 4; ++a) acc[a] *= corr;
         for (int j = 0; j < n; ++j) {
             const int key = c0 + j < n_kept ? c0 + j : lo + (c0 + j - n_kept);
             const TC* vr = vc + paged_offset(cv, seq, key, kvh);
             const float p = sc[j];
-            if (tid < hdv) acc0 = fmaf(p, to_f32<TC>(vr[tid]), acc0);
-            if (tid + 128 < hdv) acc1 = fmaf(p, to_f32<TC>(vr[tid + 128]), acc1);
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+                if (tid + 128 * a < hdv) acc[a] = fmaf(p, to_f32<TC>(vr[tid + 128 * a]), acc[a]);
         }
         __syncthreads();
     }
@@ -87,8 +100,11 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
     if (gate && !gate_wide) inv *= 1.0f / (1.0f + expf(-gate[(long long)t * g_stride + h]));
     TQ* o = out + (long long)t * o_stride + (long long)h * hdv;
     const float* gw = gate && gate_wide ? gate + (long long)t * g_stride + (long long)h * hdv : nullptr;
-    if (tid < hdv) o[tid] = from_f32<TQ>(acc0 * inv * (gw ? 1.0f / (1.0f + expf(-gw[tid])) : 1.0f));
-    if (tid + 128 < hdv) o[tid + 128] = from_f32<TQ>(acc1 * inv * (gw ? 1.0f / (1.0f + expf(-gw[tid + 128])) : 1.0f));
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int e = tid + 128 * a;
+        if (e < hdv) o[e] = from_f32<TQ>(acc[a] * inv * (gw ? 1.0f / (1.0f + expf(-gw[e])) : 1.0f));
+    }
 }
 
 // q: [T, *] with row stride q_stride (elements), heads side by side; out likewise.
@@ -97,18 +113,22 @@ UB_API int ub_attn_simple(const void* q, long long q_stride, int act_dtype, cons
                           const int* tok_pos, const int* tok_seq, const int* table, int pages_per_seq,
                           int ring, int page, int n_tokens, int nh, int nkv, int hd, int window,
                           float scale, int hd_v, int block, const float* gate, long long g_stride, int keep_first,
-                          const float* slopes, int sink, int gate_wide, float out_scale, cudaStream_t st) {
+                          const float* slopes, int sink, int gate_wide, float out_scale, float softcap,
+                          const float* dist_bias, int n_dist, const float* sink_vals, int v_row, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd_v <= 0) hd_v = hd;
-    if (hd > 256 || hd <= 0 || hd_v > 256 || nh % nkv != 0 || ring % page != 0 || nh > 65535 || block < 0) return UB_ERR_ARG;
+    if (v_row <= 0) v_row = hd_v;
+    if (hd > 1024 || hd <= 0 || hd_v > 512 || v_row < hd_v || nh % nkv != 0 || ring % page != 0 || nh > 65535 || block < 0)
+        return UB_ERR_ARG;
+    if (dist_bias && n_dist < 1) return UB_ERR_ARG;
     if (keep_first < 0 || (keep_first > 0 && block > 0)) return UB_ERR_ARG;
     PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
-    PagedKV cv{table, pages_per_seq, ring, page, nkv, hd_v};
+    PagedKV cv{table, pages_per_seq, ring, page, nkv, v_row};
     dim3 grid(n_tokens, nh);
     const size_t sm = (size_t)(hd + CHUNK) * sizeof(float);
 #define GO(TQ, TC) attn_simple_kernel<TQ, TC><<<grid, 128, sm, st>>>((const TQ*)q, q_stride, (const TC*)kcache, \
         (const TC*)vcache, (TQ*)out, o_stride, tok_pos, tok_seq, c, cv, nh, window, block, gate, g_stride, scale, \
-        keep_first, slopes, sink, gate_wide, out_scale)
+        keep_first, slopes, sink, gate_wide, out_scale, softcap, dist_bias, n_dist, sink_vals, hd_v)
     if (act_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float);
     else if (act_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16);
     else if (act_dtype == UB_F32 && cache_dtype == UB_BF16) GO(float, __nv_bfloat16);

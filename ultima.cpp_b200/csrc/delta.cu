@@ -12,7 +12,10 @@
 //   delta_prepare      short convolution + SiLU of q, k, v; unit vectors; write strength; decay
 //   conv_state_update  the convolution's last inputs, carried to the next step
 //   delta_scan         the recurrence
-//   delta_finish       per-head RMS norm of o, weight, sigmoid output gate
+//   delta_finish       per-head RMS norm of o, weight, output gate (sigmoid or SiLU of the gate's sums)
+// The decay is one number a head and key channel (its sums come in a matrix of their own, ``dpre``), or one
+// number a head whose sums are a column range of the projection row (``a_off`` >= 0; the bias then has one
+// entry a head).
 // Everything is float32; the projections come in as float32 sums of the products (for few tokens as the
 // partial sums of K slices, which the kernels add up as they read).
 #include "common.cuh"
@@ -27,6 +30,7 @@ struct DeltaShape {
     int H, G, D, E;          // heads, q/k heads, key size, value size
     int taps;                // convolution length (the last tap is the current token's)
     int q_off, k_off, v_off, b_off;   // columns of a projection row
+    int a_off;               // >= 0: one decay a head, its sums in the H columns from here on; < 0: one a key channel, from dpre
     long long ldp;           // row stride of the projections
     int n_parts;             // the projection row is the sum of this many partial results ...
     long long part_stride;   // ... this many elements apart
@@ -101,6 +105,11 @@ delta_prepare_kernel(const float* __restrict__ p, DeltaShape s, const float* __r
         vc[(long long)t * s.H * s.E + h * s.E + e] = conv_silu(s.v_off + h * s.E + e);
     if (lane == 0) beta[(long long)t * s.H + h] = sigmoidf_(proj_at(p, s, t, s.b_off + h));
     const float rate = expf(a_log[h]);
+    if (s.a_off >= 0) {
+        const float a = expf(-rate * softplusf_(proj_at(p, s, t, s.a_off + h) + dt_bias[h]));
+        for (int d = lane; d < s.D; d += 32) dec[(long long)t * s.H * s.D + h * s.D + d] = a;
+        return;
+    }
     for (int d = lane; d < s.D; d += 32) {
         const long long c = (long long)t * s.H * s.D + h * s.D + d;
         dec[c] = expf(-rate * softplusf_(dpre[c] + dt_bias[h * s.D + d]));
@@ -309,11 +318,12 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     }
 }
 
-// One warp a (token, head): o / rms(o) * w * sigmoid(z), z [T, H * E] the gate's sums.
+// One warp a (token, head): o / rms(o) * w * gate(z), z the gate's sums: H * E columns of rows ``ldz`` apart, the sum
+// of ``n_parts`` parts; gate: sigmoid(z), or (``silu_gate``) z * sigmoid(z).
 template <typename TO>
 __global__ void __launch_bounds__(128)
-delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ z, const float* __restrict__ w,
-                    TO* __restrict__ out, int n_tokens, int H, int E, float eps) {
+delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ z, long long ldz, int n_parts, long long part_stride,
+                    int silu_gate, const float* __restrict__ w, TO* __restrict__ out, int n_tokens, int H, int E, float eps) {
     pdl_trigger();
     pdl_wait();
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -326,16 +336,20 @@ delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ z, co
     for (int e = lane; e < E; e += 32) { const float v = orow[e]; ss += v * v; }
     ss = warp_sum(ss);
     const float inv = inv_rms(ss, (float)E, eps);
-    const float* zrow = z + (t * H + h) * E;
-    for (int e = lane; e < E; e += 32)
-        out[(t * H + h) * E + e] = from_f32<TO>(orow[e] * inv * w[e] * sigmoidf_(zrow[e]));
+    const float* zrow = z + t * ldz + (long long)h * E;
+    for (int e = lane; e < E; e += 32) {
+        float zv = 0.f;
+        for (int i = 0; i < n_parts; ++i) zv += zrow[i * part_stride + e];
+        const float g = silu_gate ? zv * sigmoidf_(zv) : sigmoidf_(zv);
+        out[(t * H + h) * E + e] = from_f32<TO>(orow[e] * inv * w[e] * g);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
-// shape: [H, G, D, E, taps, q_off, k_off, v_off, b_off] (9 ints)
+// shape: [H, G, D, E, taps, q_off, k_off, v_off, b_off, a_off] (10 ints)
 static int read_shape(const int* shape, long long ldp, int n_parts, long long part_stride, DeltaShape& s) {
     s.H = shape[0]; s.G = shape[1]; s.D = shape[2]; s.E = shape[3]; s.taps = shape[4];
-    s.q_off = shape[5]; s.k_off = shape[6]; s.v_off = shape[7]; s.b_off = shape[8];
+    s.q_off = shape[5]; s.k_off = shape[6]; s.v_off = shape[7]; s.b_off = shape[8]; s.a_off = shape[9];
     s.ldp = ldp; s.n_parts = n_parts; s.part_stride = part_stride;
     if (s.H <= 0 || s.G <= 0 || s.H % s.G || s.D <= 0 || s.D > 256 || s.E <= 0 || s.taps < 1 || s.taps > MAX_TAPS ||
         s.H > 65535 || n_parts < 1) return UB_ERR_ARG;
@@ -399,16 +413,17 @@ UB_API int ub_delta_scan(const float* qn, const float* kn, const float* vc, cons
     return (int)e;
 }
 
-UB_API int ub_delta_finish(const float* o, const float* z, const float* w, void* out, int out_dtype, int n_tokens, int H,
-                           int E, float eps, cudaStream_t st) {
+UB_API int ub_delta_finish(const float* o, const float* z, long long ldz, int n_parts, long long part_stride, int silu_gate,
+                           const float* w, void* out, int out_dtype, int n_tokens, int H, int E, float eps, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
+    if (n_parts < 1) return UB_ERR_ARG;
     const long long warps = (long long)n_tokens * H;
     const unsigned grid = (unsigned)((warps + 3) / 4);
     cudaError_t e;
     if (out_dtype == UB_F32)
-        e = ub_launch_dependent(delta_finish_kernel<float>, dim3(grid), dim3(128), 0, st, o, z, w, (float*)out, n_tokens, H, E, eps);
+        e = ub_launch_dependent(delta_finish_kernel<float>, dim3(grid), dim3(128), 0, st, o, z, ldz, n_parts, part_stride, silu_gate, w, (float*)out, n_tokens, H, E, eps);
     else if (out_dtype == UB_BF16)
-        e = ub_launch_dependent(delta_finish_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, o, z, w, (__nv_bfloat16*)out, n_tokens, H, E, eps);
+        e = ub_launch_dependent(delta_finish_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, o, z, ldz, n_parts, part_stride, silu_gate, w, (__nv_bfloat16*)out, n_tokens, H, E, eps);
     else return UB_ERR_UNSUPPORTED;
     return (int)e;
 }

@@ -7,21 +7,48 @@
 // (src/model/weight_dispatch.cpp:374-441, src/kernels/dot_batched.cpp:39-96).
 // The k order of every output's sum is the same whatever the number of rows, so a token's
 // result does not depend on what else is in the batch.
+//
+// Two further forms of the same kernel.  Batched (``ub_gemm_simt_batched``): grid.z products with the
+// same sizes, operands and results a fixed number of elements apart (one small matrix a head).  Grouped
+// (``ub_gemm_simt_grouped``): rows that were sorted by the matrix they meet (a routed feed-forward's experts):
+// ``tiles`` lists, for each block of up to 64 sorted rows, (matrix, first row, rows); the number of tiles in use is
+// read on the device, blocks beyond it return; ``src_rows`` (optional) names, for a sorted row, the row of A it is.
 #include "common.cuh"
 
 enum : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 
 constexpr int BM = 64, BN = 64, BK = 16;
 
+struct SimtExtra {
+    long long a_bs, w_bs, o_bs;     // batched: elements between one product's operands and the next one's; grouped: w_bs between matrices
+    const int4* tiles;              // grouped: (matrix, first sorted row, rows, unused) for every block of rows
+    const int* n_tiles;             // grouped: tiles in use (on the device)
+    const int* src_rows;            // grouped, optional: the row of A behind a sorted row
+};
+
 template <typename TA, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const TW* __restrict__ W2,
-                 TO* __restrict__ out, int M, int N, int K, long long lda, long long ldw, long long ldo) {
+                 TO* __restrict__ out, int M, int N, int K, long long lda, long long ldw, long long ldo, SimtExtra ex) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     __shared__ float W2s[EPI == EPI_SWIGLU ? BK : 1][BN + 4];
     const int tid = threadIdx.x;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    int m0 = blockIdx.y * BM;
+    const int n0 = blockIdx.x * BN;
+    if (ex.tiles) {
+        if ((int)blockIdx.y >= *ex.n_tiles) return;
+        const int4 ti = ex.tiles[blockIdx.y];
+        W += ti.x * ex.w_bs;
+        if (EPI == EPI_SWIGLU) W2 += ti.x * ex.w_bs;
+        m0 = ti.y;
+        M = ti.y + ti.z;
+    } else {
+        A += blockIdx.z * ex.a_bs;
+        W += blockIdx.z * ex.w_bs;
+        if (EPI == EPI_SWIGLU) W2 += blockIdx.z * ex.w_bs;
+        out += blockIdx.z * ex.o_bs;
+    }
     const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
     float acc[4][4] = {}, acc2[4][4] = {};
     for (int k0 = 0; k0 < K; k0 += BK) {
@@ -33,7 +60,7 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const TW* _
             const int k = k0 + kk;
             float a = 0.f, w = 0.f, w2 = 0.f;
             if (k < K) {
-                if (m0 + r < M) a = to_f32<TA>(A[(long long)(m0 + r) * lda + k]);
+                if (m0 + r < M) a = to_f32<TA>(A[(long long)(ex.src_rows ? ex.src_rows[m0 + r] : m0 + r) * lda + k]);
                 if (n0 + r < N) {
                     w = to_f32<TW>(W[(long long)(n0 + r) * ldw + k]);
                     if (EPI == EPI_SWIGLU) w2 = to_f32<TW>(W2[(long long)(n0 + r) * ldw + k]);
@@ -81,10 +108,12 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const TW* _
 
 template <typename TA, typename TW, typename TO>
 static int launch(const void* A, const void* W, const void* W2, void* out, int M, int N, int K,
-                  long long lda, long long ldw, long long ldo, int epi, cudaStream_t st) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    if (grid.y > 65535) return UB_ERR_ARG;
-#define GO(E) gemm_simt_kernel<TA, TW, TO, E><<<grid, 256, 0, st>>>((const TA*)A, (const TW*)W, (const TW*)W2, (TO*)out, M, N, K, lda, ldw, ldo)
+                  long long lda, long long ldw, long long ldo, int epi, cudaStream_t st, SimtExtra ex = SimtExtra{},
+                  int batch = 1, int max_tiles = 0) {
+    dim3 grid((N + BN - 1) / BN, ex.tiles ? max_tiles : (M + BM - 1) / BM, batch);
+    if (grid.y > 65535 || grid.z > 65535) return UB_ERR_ARG;
+    if (grid.y == 0) return 0;
+#define GO(E) gemm_simt_kernel<TA, TW, TO, E><<<grid, 256, 0, st>>>((const TA*)A, (const TW*)W, (const TW*)W2, (TO*)out, M, N, K, lda, ldw, ldo, ex)
     if (epi == EPI_STORE) GO(EPI_STORE);
     else if (epi == EPI_ADD) GO(EPI_ADD);
     else if (epi == EPI_SWIGLU) { if (!W2) return UB_ERR_ARG; GO(EPI_SWIGLU); }
@@ -92,6 +121,47 @@ static int launch(const void* A, const void* W, const void* W2, void* out, int M
 #undef GO
     UB_LAUNCH_CHECK();
     return 0;
+}
+
+static int dispatch(const void* A, int a_dtype, const void* W, const void* W2, int w_dtype, void* out, int o_dtype, int M, int N,
+                    int K, long long lda, long long ldw, long long ldo, int epi, cudaStream_t st, SimtExtra ex, int batch,
+                    int max_tiles) {
+    if (K <= 0) return UB_ERR_ARG;
+    if (epi == EPI_ADD && o_dtype != UB_F32) return UB_ERR_ARG;
+    const int key = a_dtype * 4 + w_dtype * 2 + o_dtype;
+#define CASE(n, TA, TW, TO) case n: return launch<TA, TW, TO>(A, W, W2, out, M, N, K, lda, ldw, ldo, epi, st, ex, batch, max_tiles)
+    switch (key) {
+        CASE(0, float, float, float);
+        CASE(1, float, float, __nv_bfloat16);
+        CASE(2, float, __nv_bfloat16, float);
+        CASE(3, float, __nv_bfloat16, __nv_bfloat16);
+        CASE(4, __nv_bfloat16, float, float);
+        CASE(5, __nv_bfloat16, float, __nv_bfloat16);
+        CASE(6, __nv_bfloat16, __nv_bfloat16, float);
+        CASE(7, __nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    }
+#undef CASE
+    return UB_ERR_UNSUPPORTED;
+}
+
+// ``batch`` products out_b = A_b W_b^T, operands and results a_bs, w_bs, o_bs elements apart.
+UB_API int ub_gemm_simt_batched(const void* A, int a_dtype, const void* W, int w_dtype, void* out, int o_dtype, int M, int N,
+                                int K, long long lda, long long ldw, long long ldo, int batch, long long a_bs, long long w_bs,
+                                long long o_bs, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    SimtExtra ex{a_bs, w_bs, o_bs, nullptr, nullptr, nullptr};
+    return dispatch(A, a_dtype, W, nullptr, w_dtype, out, o_dtype, M, N, K, lda, ldw, ldo, EPI_STORE, st, ex, batch, 0);
+}
+
+// Sorted rows against the matrix each tile names: out[sorted row, :] = A[src_rows[sorted row] or the row, :] W_e^T (with
+// EPI_SWIGLU the second matrix W2_e is the same distance from W2).  ``max_tiles``: the most tiles the launch can need.
+UB_API int ub_gemm_simt_grouped(const void* A, int a_dtype, const void* W, const void* W2, int w_dtype, void* out, int o_dtype,
+                                int N, int K, long long lda, long long ldw, long long ldo, long long w_bs, const void* tiles,
+                                const int* n_tiles, const int* src_rows, int max_tiles, int epi, cudaStream_t st) {
+    if (N <= 0 || max_tiles <= 0) return 0;
+    if (!tiles || !n_tiles || epi == EPI_ADD) return UB_ERR_ARG;
+    SimtExtra ex{0, w_bs, 0, (const int4*)tiles, n_tiles, src_rows};
+    return dispatch(A, a_dtype, W, W2, w_dtype, out, o_dtype, 0, N, K, lda, ldw, ldo, epi, st, ex, 1, max_tiles);
 }
 
 // a_dtype, w_dtype, o_dtype: UB_F32 / UB_BF16.  EPI_ADD needs a float32 output.

@@ -1,0 +1,196 @@
+// A routed feed-forward (mixture of experts): which experts a token uses, the order its rows are worked in,
+// and the weighted sum of what the experts return.  The experts' products themselves are grouped matrix
+// products over the sorted rows (gemm_simt.cu, gemm_mma.cu).
+//
+//   route     one warp a token: s = softmax(z) over all router outputs (float32); choice scores s + correction;
+//             with groups, only the outputs of the ``keep`` groups with the largest choice score stay (the
+//             others count as -inf); the ``top`` largest choice scores are chosen, lowest index first among
+//             equals; a chosen output's weight is its s (no renormalisation).  Outputs from ``n_experts`` on
+//             are identity experts.  Counts the rows of every real expert.
+//   plan      one block: the experts' segments of the sorted rows (first row of each), the tiles of up to
+//             ``tile`` rows (expert, first row, rows) that the grouped products run over, their number; clears
+//             the counters for the next use.
+//   scatter   one thread a (token, choice): its place in its expert's segment (``row_pos``; -1 for an identity
+//             expert) and, for that place, the token it is (``src_rows``).
+//   combine   one block a token: residual += sum_k w_k * (expert row k, or the token's own input for an
+//             identity expert), in the order of k.
+// Places within a segment are handed out by an atomic counter, so they differ from run to run; every row of a
+// product is computed on its own, so no result depends on them.
+#include "common.cuh"
+
+constexpr int ROUTE_WARPS = 4;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_kernel(const float* __restrict__ z, long long ldz, const float* __restrict__ corr, int n_tokens, int n_out, int n_experts,
+             int top, int n_groups, int keep, int* __restrict__ idx, float* __restrict__ wts, int* __restrict__ counts) {
+    extern __shared__ float sm[];
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = (long long)blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= n_tokens) return;
+    float* sc = sm + (size_t)warp * (2 * n_out + n_groups);      // scores
+    float* ch = sc + n_out;                                      // choice scores
+    float* gm = ch + n_out;                                      // a group's best choice score
+    const float* zr = z + t * ldz;
+    float m = -INFINITY;
+    for (int i = lane; i < n_out; i += 32) m = fmaxf(m, zr[i]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int i = lane; i < n_out; i += 32) { const float e = expf(zr[i] - m); sc[i] = e; sum += e; }
+    sum = warp_sum(sum);
+    for (int i = lane; i < n_out; i += 32) { const float s = sc[i] / sum; sc[i] = s; ch[i] = s + (corr ? corr[i] : 0.f); }
+    __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        const int size = n_out / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float b = -INFINITY;
+            for (int i = 0; i < size; ++i) b = fmaxf(b, ch[g * size + i]);
+            gm[g] = b;
+        }
+        __syncwarp();
+        // the kept groups are marked with +inf; what is left unmarked loses its outputs
+        for (int r = 0; r < keep; ++r) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gm[g];
+                if (v != INFINITY && (v > best || (v == best && g < at))) { best = v; at = g; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (lane == 0 && at != 0x7fffffff) gm[at] = INFINITY;
+            __syncwarp();
+        }
+        for (int i = lane; i < n_out; i += 32)
+            if (gm[i / size] != INFINITY) ch[i] = -INFINITY;
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int i = lane; i < n_out; i += 32) {
+            const float v = ch[i];
+            if (!isnan(v) && (v > best || (v == best && i < at))) { best = v; at = i; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at == 0x7fffffff) at = 0;                     // (every score was taken or not a number: a row of NaN)
+        if (lane == 0) {
+            idx[t * top + k] = at;
+            wts[t * top + k] = sc[at];
+            ch[at] = NAN;                                 // taken: NaN is passed over, while -inf may still be chosen
+            if (at < n_experts) atomicAdd(&counts[at], 1);
+        }
+        __syncwarp();
+    }
+}
+
+__global__ void plan_kernel(int* __restrict__ counts, int* __restrict__ cursor, int* __restrict__ seg_start,
+                            int4* __restrict__ tiles, int* __restrict__ n_tiles, int n_experts, int tile) {
+    extern __shared__ int sh[];          // [n_experts] counts, [n_experts + 1] first tile of each expert
+    pdl_trigger();
+    pdl_wait();
+    int* cnt = sh;
+    int* first_tile = sh + n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) { cnt[e] = counts[e]; counts[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int row = 0, tl = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            seg_start[e] = row;
+            first_tile[e] = tl;
+            row += cnt[e];
+            tl += (cnt[e] + tile - 1) / tile;
+        }
+        first_tile[n_experts] = tl;
+        *n_tiles = tl;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int n = cnt[e], r0 = seg_start[e];
+        for (int i = 0; i * tile < n; ++i) tiles[first_tile[e] + i] = make_int4(e, r0 + i * tile, min(tile, n - i * tile), 0);
+    }
+}
+
+__global__ void scatter_kernel(const int* __restrict__ idx, const int* __restrict__ seg_start, int* __restrict__ cursor,
+                               int* __restrict__ row_pos, int* __restrict__ src_rows, long long n, int top, int n_experts) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int e = idx[i];
+    if (e >= n_experts) { row_pos[i] = -1; return; }
+    const int p = seg_start[e] + atomicAdd(&cursor[e], 1);
+    row_pos[i] = p;
+    src_rows[p] = (int)(i / top);
+}
+
+template <typename TH, typename TY>
+__global__ void combine_kernel(const TY* __restrict__ y, const TH* __restrict__ h, const int* __restrict__ row_pos,
+                               const float* __restrict__ wts, float* __restrict__ residual, int width, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int p = row_pos[t * top + k];
+            const float v = p >= 0 ? to_f32<TY>(y[(long long)p * width + c]) : to_f32<TH>(h[t * width + c]);
+            acc = fmaf(wts[t * top + k], v, acc);
+        }
+        residual[t * width + c] += acc;
+    }
+}
+
+UB_API int ub_route(const float* z, long long ldz, const float* corr, int n_tokens, int n_out, int n_experts, int top,
+                    int n_groups, int keep, int* idx, float* wts, int* counts, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (n_out < 1 || n_experts < 0 || n_experts > n_out || top < 1 || top > n_out || n_groups < 1 || n_out % n_groups ||
+        keep < 1 || keep > n_groups) return UB_ERR_ARG;
+    const size_t smem = (size_t)ROUTE_WARPS * (2 * n_out + n_groups) * sizeof(float);
+    if (smem > 48 * 1024) return UB_ERR_ARG;
+    const unsigned grid = (unsigned)((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS);
+    return (int)ub_launch_dependent(route_kernel, dim3(grid), dim3(ROUTE_WARPS * 32), smem, st, z, ldz, corr, n_tokens, n_out,
+                                    n_experts, top, n_groups, keep, idx, wts, counts);
+}
+
+UB_API int ub_route_plan(int* counts, int* cursor, int* seg_start, void* tiles, int* n_tiles, int n_experts, int tile,
+                         cudaStream_t st) {
+    if (n_experts < 1 || tile < 1) return UB_ERR_ARG;
+    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
+    if (smem > 48 * 1024) return UB_ERR_ARG;
+    return (int)ub_launch_dependent(plan_kernel, dim3(1), dim3(256), smem, st, counts, cursor, seg_start, (int4*)tiles, n_tiles,
+                                    n_experts, tile);
+}
+
+UB_API int ub_route_scatter(const int* idx, const int* seg_start, int* cursor, int* row_pos, int* src_rows, int n_tokens,
+                            int top, int n_experts, cudaStream_t st) {
+    const long long n = (long long)n_tokens * top;
+    if (n <= 0) return 0;
+    return (int)ub_launch_dependent(scatter_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, idx, seg_start, cursor,
+                                    row_pos, src_rows, n, top, n_experts);
+}
+
+// y: the experts' results for the sorted rows [rows, width] (float32 or bfloat16); h: the feed-forward's input
+// [tokens, width], which an identity expert hands on.
+UB_API int ub_route_combine(const void* y, int y_dtype, const void* h, int h_dtype, const int* row_pos, const float* wts,
+                            float* residual, int n_tokens, int width, int top, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    cudaError_t e;
+#define GO(TH, TY) e = ub_launch_dependent(combine_kernel<TH, TY>, dim3(n_tokens), dim3(threads), 0, st, (const TY*)y, (const TH*)h, \
+                                           row_pos, wts, residual, width, top)
+    if (h_dtype == UB_F32 && y_dtype == UB_F32) GO(float, float);
+    else if (h_dtype == UB_BF16 && y_dtype == UB_F32) GO(__nv_bfloat16, float);
+    else if (h_dtype == UB_BF16 && y_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+    else return UB_ERR_UNSUPPORTED;
+#undef GO
+    return (int)e;
+}

@@ -117,11 +117,19 @@ class Model:
             x = self.embedding.forward(batch.tok_ids, rt)
         if TRACE:
             _trace("embd", 0, x)
+        S = int(self.spec.streams or 0)
+        if S > 0:
+            # the stream in S copies, all equal to the embedding's output; layers take [S, T, width]
+            from ..kernels import ops
+            copies = rt.arena.alloc((S,) + tuple(x.shape), x.dtype)
+            rt.launches += 1
+            ops.streams_fill(x, copies)
+            x = copies
         x0 = None
         if self._keeps_embedding:
             x0 = rt.arena.alloc(tuple(x.shape), x.dtype)
             x0.copy_(x)
-        plan = self._stack_plan(cache) if (batch.max_new == 1 and batch.n_tokens <= 64) else None
+        plan = self._stack_plan(cache) if (batch.max_new == 1 and batch.n_tokens <= 64 and S == 0) else None
         if plan is not None:
             plan.run(x, batch)                    # one token a sequence: the whole stack in one kernel
         else:
@@ -133,8 +141,15 @@ class Model:
                 if TRACE:
                     _trace("l_out", i, x)
                 if self.tap is not None:
-                    self.tap(i, x)
+                    self.tap(i, x if S == 0 else x.sum(0))
         if batch.want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
+        if S > 0:
+            # the copies are summed where the final norm reads them, at the wanted rows only
+            from ..kernels import ops
+            h = rt.arena.alloc((batch.want_rows.numel(), self.spec.width), rt.dtype)
+            rt.launches += 1
+            ops.streams_pass(x, read=(None, self.final_norm.weight, self.final_norm.eps), out=h, rows=batch.want_rows)
+            return self.head.forward(h, rt)
         h = self.final_norm.forward(x, rt, rows=batch.want_rows)
         return self.head.forward(h, rt)

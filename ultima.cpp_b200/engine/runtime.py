@@ -145,7 +145,46 @@ class Runtime:
         gemm_tc.gemm(a, w, out, ops.EPI_STORE, None, self, splits=parts)
         return out
 
+    def matmul_heads(self, a, w, out):
+        """out[:, b, :] = a[:, b, :] @ w[b].T for every b (one small matrix a head): a [T, B, K], w [B, N, K], out
+        [T, B, N]; a and out may be column ranges of wider rows."""
+        self.launches += 1
+        if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+            from ..kernels import gemm_mma
+            if gemm_mma.accepts_batched(a, w, out):
+                return gemm_mma.batched(a, w, out)
+        return ops.gemm_batched(a, w, out)
+
+    def matmul_grouped(self, a, w, out, plan, epilogue=ops.EPI_STORE, w2=None):
+        """Sorted rows against the matrix their tile names (``plan``: a routed feed-forward's ``RoutePlan``):
+        out[p] = a[plan.src_rows[p] or p] @ w[e].T, e the expert of the tile that holds sorted row p."""
+        self.launches += 1
+        if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            from ..kernels import gemm_mma
+            if gemm_mma.accepts_grouped(a, w, out, epilogue):
+                return gemm_mma.grouped(a, w, out, plan, epilogue, w2)
+        return ops.gemm_grouped(a, w, out, plan.tiles, plan.n_tiles, plan.src_rows if plan.gather else None, plan.max_tiles,
+                                epilogue, w2)
+
     # ---- attention ----------------------------------------------------------------------
+    def attention_latent(self, q_lat, kv, batch, n_heads, row, rank, scale, window):
+        """Attention of ``n_heads`` query heads [T, heads, row] over ONE key head whose rows [row] also hold the values
+        (their leading ``rank`` columns).  Returns the heads' weighted sums as a view [T, heads, rank] (of a wider
+        buffer where the kernel returns whole rows)."""
+        T = q_lat.shape[0]
+        q2 = q_lat.view(T, n_heads * row)
+        self.launches += 1
+        if self.use_tensor_cores and q_lat.dtype == torch.bfloat16:
+            from ..kernels import attn_tc
+            if attn_tc.accepts(q2, kv, row, n_heads, 1) and attn_tc.LATENT:
+                o = self.arena.alloc((T, n_heads, row), self.dtype)
+                attn_tc.attention(q2, kv, o.view(T, n_heads * row), batch, n_heads, 1, row, scale, self, kernel="mma")
+                return o[:, :, :rank]
+        o = self.arena.alloc((T, n_heads, rank), self.dtype)
+        ops.attn_simple(q2, kv.k, kv.k, o.view(T, n_heads * rank), batch.tok_pos, batch.tok_seq, kv.table, kv.ring, kv.page,
+                        n_heads, 1, row, window, scale, v_head_dim=rank, v_row=row)
+        return o
+
     def attention_from_qkv(self, qkv_parts, q_norm, k_norm, cos, sin, eps, kv, out, batch, n_heads, n_kv_heads,
                            head_dim, scale) -> bool:
         """Attention of a step of one token a sequence, straight from the float32 partial results of

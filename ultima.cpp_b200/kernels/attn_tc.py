@@ -157,6 +157,17 @@ def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window, per_sm: in
     return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
 
 
+# ULTIMA_ATTN_LATENT=0: latent attention stays on the any-shape kernel
+LATENT = _os.environ.get("ULTIMA_ATTN_LATENT", "1") != "0"
+
+
+def latent_needs(row: int, n_heads: int) -> list:
+    """The libraries latent attention over key rows of ``row`` numbers uses beyond the any-shape kernel."""
+    if LATENT and row % 16 == 0 and 16 <= row <= 256:
+        return [target(row)]
+    return []
+
+
 FUSE_QKV = _os.environ.get("ULTIMA_ATTN_FUSE_QKV", "1") != "0"
 
 

@@ -114,8 +114,17 @@ def _declare(lib, source: str) -> None:
             "ub_add_rows": [P, P, P, I, I, P],
             "ub_elem_gate": [P, I, L, P, L, I, I, F, P],
         },
-        "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P]},
-        "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, I, P, I, I, F, P],
+        "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P],
+                         "ub_gemm_simt_batched": [P, I, P, I, P, I, I, I, I, L, L, L, I, L, L, L, P],
+                         "ub_gemm_simt_grouped": [P, I, P, P, I, P, I, I, I, L, L, L, L, P, P, P, I, I, P]},
+        "streams.cu": {"ub_streams_fill": [P, P, I, I, I, P],
+                       "ub_streams_pass": [P, L, I, P, P, P, P, I, P, P, P, I, I, I, F, P]},
+        "routed.cu": {"ub_route": [P, L, P, I, I, I, I, I, I, P, P, P, P],
+                      "ub_route_plan": [P, P, P, P, P, I, I, P],
+                      "ub_route_scatter": [P, P, P, P, P, I, I, I, P],
+                      "ub_route_combine": [P, I, P, I, P, P, P, I, I, I, P]},
+        "latent.cu": {"ub_latent_place": [P, I, L, I, L, I, I, P, P, I, P, P, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P]},
+        "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, I, P, I, I, F, F, P, I, P, I, P],
                            "ub_qkv_place_rows": [P, I, L, I, L, I, I, I, P, I, L, P, P, I, P, P, I, I, P, P, P, P, I, P, I, I, I, I, I,
                                                  I, I, I, F, I, I, P, P],
                            "ub_qkv_place": [P, I, L, I, L, I, I, I, P, I, L, P, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I,
@@ -123,7 +132,7 @@ def _declare(lib, source: str) -> None:
         "delta.cu": {"ub_delta_prepare": [P, L, I, L, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
                      "ub_conv_state_update": [P, L, I, L, P, P, P, I, I, I, P],
                      "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
-                     "ub_delta_finish": [P, P, P, P, I, I, I, I, F, P]},
+                     "ub_delta_finish": [P, P, L, I, L, I, P, P, I, I, I, I, F, P]},
         "ssm.cu": {"ub_ssm_prepare": [P, L, I, L, P, P, P, P, I, P, P, P, P, P, P, P, P, I, P],
                    "ub_ssm_conv_state_update": [P, L, I, L, P, P, P, P, I, P],
                    "ub_ssm_scan": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
@@ -370,14 +379,21 @@ def gemm_simt(a, w, out, epilogue=EPI_STORE, w2=None):
 
 def attn_simple(q, k_cache, v_cache, out, tok_pos, tok_seq, table, ring, page, n_heads,
                 n_kv_heads, head_dim, window, scale, v_head_dim=None, block=None, gate=None, keep_first=0, slopes=None,
-                sink=False, out_scale=1.0):
+                sink=False, out_scale=1.0, softcap=None, dist_bias=None, sink_vals=None, v_row=None):
     """Attention of every token of the step over its sequence's cached keys and values.  ``v_head_dim``:
     the values' head size where it differs; ``block``: positions are masked in blocks of this many,
     counted from the sequence's start; ``gate`` float32 [T, heads] or [T, heads * value size]: the output
     times its sigmoid, head by head or element by element; ``keep_first``: positions that stay visible
     behind the window; ``slopes`` float32 [heads]: slope * distance is taken off a score; ``sink``: one
-    more term exp(0) in the softmax's sum; ``out_scale`` multiplies the output."""
-    _need_cuda(q, k_cache, v_cache, out, table, gate, slopes)
+    more term exp(0) in the softmax's sum (``sink_vals`` float32 [heads]: exp(sink_vals[h]) instead);
+    ``out_scale`` multiplies the output; ``softcap``: a scaled score s becomes softcap * tanh(s / softcap);
+    ``dist_bias`` float32 [distances, heads]: the row of min(distance, rows - 1) is added to the score behind the
+    cap; ``v_row``: the width of a row of ``v_cache`` where it is more than the values' head size (values that
+    are the leading columns of the key rows)."""
+    _need_cuda(q, k_cache, v_cache, out, table, gate, slopes, dist_bias, sink_vals)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.dim() == 2
+                                 and dist_bias.shape[1] == n_heads)
+    assert sink_vals is None or (sink_vals.dtype == torch.float32 and sink_vals.is_contiguous() and sink_vals.numel() == n_heads)
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype
     assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
@@ -391,8 +407,9 @@ def attn_simple(q, k_cache, v_cache, out, tok_pos, tok_seq, table, ring, page, n
         _ptr(q), q.stride(0), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
         out.stride(0), _ptr(tok_pos), _ptr(tok_seq), _ptr(table), table.shape[1], ring, page, T,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), int(v_head_dim or head_dim), int(block or 0),
-        _ptr(gate), gate.stride(0) if gate is not None else 0, int(keep_first or 0), _ptr(slopes), 1 if sink else 0,
-        gate_wide, float(out_scale), _stream()), "attn_simple")
+        _ptr(gate), gate.stride(0) if gate is not None else 0, int(keep_first or 0), _ptr(slopes),
+        1 if (sink or sink_vals is not None) else 0, gate_wide, float(out_scale), float(softcap or 0.0), _ptr(dist_bias),
+        dist_bias.shape[0] if dist_bias is not None else 0, _ptr(sink_vals), int(v_row or 0), _stream()), "attn_simple")
 
 
 def qkv_place(x, q_off, k_off, v_off, q_out, q_weight, k_weight, cos, sin, rotary_dim, tok_pos, tok_seq, k_cache,
@@ -460,6 +477,137 @@ def qkv_place_rows(x, q_off, k_off, v_off, q_out, q_weight, k_weight, norm_whole
 
 
 # ---------------------------------------------------------------------------------------
+# several copies of the residual stream (csrc/streams.cu)
+def streams_fill(x, xs):
+    """Every copy xs[s] (float32 [S, T, width]) becomes x (float32 [T, width])."""
+    _need_cuda(x, xs)
+    assert x.dtype == xs.dtype == torch.float32 and x.is_contiguous() and xs.is_contiguous() and xs.shape[1:] == x.shape
+    _check(_lib("streams.cu").ub_streams_fill(_ptr(x), _ptr(xs), x.shape[0], x.shape[1], xs.shape[0], _stream()), "streams_fill")
+
+
+def streams_pass(xs, write=None, read=None, out=None, rows=None):
+    """One pass over the copies xs (float32 [S, T, width]), row by row.  ``write`` = (mix [S, S] indexed [from, to],
+    b [S], y [T, width]): xs'[t] = sum_s mix[s, t] xs[s] + b[t] y, and y is cleared.  ``read`` = (a [S] or None for the
+    plain sum, norm weight [width] or None for no norm, eps): ``out`` [T or len(rows), width] receives
+    norm(sum_s a[s] xs[s]) of the (new) copies; ``rows`` (int32) picks the rows that are read (no write then)."""
+    _need_cuda(xs, out, rows)
+    S, T, width = xs.shape
+    assert xs.dtype == torch.float32 and xs.is_contiguous()
+    mix = b = y = a = w = None
+    eps = 0.0
+    if write is not None:
+        mix, b, y = write
+        for t, n in ((mix, S * S), (b, S)):
+            assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n
+        assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, width) and rows is None
+    n_rows = T
+    if read is not None:
+        a, w, eps = read
+        assert a is None or (a.dtype == torch.float32 and a.is_contiguous() and a.numel() == S)
+        assert w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == width)
+        n_rows = T if rows is None else rows.numel()
+        assert out is not None and out.is_contiguous() and out.shape == (n_rows, width)
+        assert rows is None or rows.dtype == torch.int32
+    _check(_lib("streams.cu").ub_streams_pass(_ptr(xs), xs.stride(0), S, _ptr(mix), _ptr(b), _ptr(y), _ptr(a),
+                                              1 if read is not None else 0, _ptr(w), _ptr(rows), _ptr(out),
+                                              _code(out) if out is not None else F32, n_rows, width, float(eps), _stream()),
+           "streams_pass")
+
+
+# ---------------------------------------------------------------------------------------
+# products of many small matrices (csrc/gemm_simt.cu)
+def gemm_batched(a, w, out):
+    """out[:, b, :] = a[:, b, :] @ w[b].T for every b: a [T, B, K], w [B, N, K] contiguous, out [T, B, N]; a and out
+    may be column ranges of wider rows (any row and batch stride, last stride 1).  CUDA cores, float32 sums in k order."""
+    _need_cuda(a, w, out)
+    T, B, K = a.shape
+    N = w.shape[1]
+    assert w.shape == (B, N, K) and w.is_contiguous() and out.shape == (T, B, N) and a.stride(2) == 1 and out.stride(2) == 1
+    _check(_lib("gemm_simt.cu").ub_gemm_simt_batched(_ptr(a), _code(a), _ptr(w), _code(w), _ptr(out), _code(out), T, N, K,
+                                                     a.stride(0), K, out.stride(0), B, a.stride(1), N * K, out.stride(1),
+                                                     _stream()), "gemm_batched")
+
+
+def gemm_grouped(a, w, out, tiles, n_tiles, src_rows, max_tiles, epilogue=EPI_STORE, w2=None):
+    """Sorted rows against the matrix their tile names: out[p, :] = a[src_rows[p] (or p), :] @ w[e].T; w [E, N, K]
+    contiguous; EPI_SWIGLU: out = silu(a w[e]^T) * (a w2[e]^T), w2 a view with w's strides.  ``tiles`` int32
+    [max_tiles, 4] (matrix, first row, rows, -) and ``n_tiles`` int32 [1] on the device (csrc/routed.cu makes them)."""
+    _need_cuda(a, w, out, tiles, n_tiles, src_rows)
+    E, N, K = w.shape
+    assert w.stride(2) == 1 and w.stride(1) >= K and a.stride(1) == 1 and out.stride(1) == 1 and out.shape[1] == N and a.shape[1] == K
+    assert tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 4 * max_tiles
+    if w2 is not None:
+        assert w2.shape == w.shape and w2.stride() == w.stride() and w2.dtype == w.dtype
+    _check(_lib("gemm_simt.cu").ub_gemm_simt_grouped(_ptr(a), _code(a), _ptr(w), _ptr(w2), _code(w), _ptr(out), _code(out), N, K,
+                                                     a.stride(0), w.stride(1), out.stride(0), w.stride(0), _ptr(tiles),
+                                                     _ptr(n_tiles), _ptr(src_rows), int(max_tiles), epilogue, _stream()),
+           "gemm_grouped")
+
+
+# ---------------------------------------------------------------------------------------
+# the routed feed-forward (csrc/routed.cu)
+ROUTE_TILE = 64          # sorted rows a tile of the grouped products
+
+
+def route(z, correction, n_experts, top, n_groups, keep, idx, wts, counts):
+    """z float32 [T, outputs] router logits -> idx int32 [T, top], wts float32 [T, top]; counts int32 [n_experts] += rows."""
+    _need_cuda(z, correction, idx, wts, counts)
+    T, n_out = z.shape
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and idx.dtype == torch.int32 and wts.dtype == torch.float32
+    assert idx.is_contiguous() and wts.is_contiguous() and idx.shape == wts.shape == (T, top) and counts.dtype == torch.int32
+    assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == n_out)
+    _check(_lib("routed.cu").ub_route(_ptr(z), z.stride(0), _ptr(correction), T, n_out, n_experts, top, n_groups, keep,
+                                      _ptr(idx), _ptr(wts), _ptr(counts), _stream()), "route")
+
+
+def route_plan(counts, cursor, seg_start, tiles, n_tiles, n_experts, tile=ROUTE_TILE):
+    _need_cuda(counts, cursor, seg_start, tiles, n_tiles)
+    for t in (counts, cursor, seg_start, tiles, n_tiles):
+        assert t.dtype == torch.int32 and t.is_contiguous()
+    _check(_lib("routed.cu").ub_route_plan(_ptr(counts), _ptr(cursor), _ptr(seg_start), _ptr(tiles), _ptr(n_tiles), n_experts,
+                                           tile, _stream()), "route_plan")
+
+
+def route_scatter(idx, seg_start, cursor, row_pos, src_rows, n_experts):
+    _need_cuda(idx, seg_start, cursor, row_pos, src_rows)
+    T, top = idx.shape
+    assert row_pos.dtype == src_rows.dtype == torch.int32 and row_pos.numel() == T * top and src_rows.numel() >= T * top
+    _check(_lib("routed.cu").ub_route_scatter(_ptr(idx), _ptr(seg_start), _ptr(cursor), _ptr(row_pos), _ptr(src_rows), T, top,
+                                              n_experts, _stream()), "route_scatter")
+
+
+def route_combine(y, h, row_pos, wts, residual):
+    """residual[t] += sum_k wts[t, k] * (y[row_pos[t, k]] or, where row_pos is -1, h[t])."""
+    _need_cuda(y, h, row_pos, wts, residual)
+    T, width = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and h.is_contiguous() and h.shape == (T, width)
+    assert y.is_contiguous() and y.shape[1] == width
+    _check(_lib("routed.cu").ub_route_combine(_ptr(y), _code(y), _ptr(h), _code(h), _ptr(row_pos), _ptr(wts), _ptr(residual),
+                                              T, width, wts.shape[1], _stream()), "route_combine")
+
+
+# ---------------------------------------------------------------------------------------
+# latent attention (csrc/latent.cu)
+def latent_place(x, q_off, c_off, q_plain, q_lat, c_weight, cos, sin, rotary_dim, tok_pos, tok_seq, k_cache, table, ring, page,
+                 n_heads, dim, rot, rank, eps):
+    """From projection rows x ([T, N] or [parts, T, N], summed): the heads' unrotated query parts into q_plain
+    [T, heads, dim], their rotated parts into q_lat[:, :, rank:] ([T, heads, rank + rot]), and the position's cache row
+    [normed latent | rotated key part]."""
+    _need_cuda(x, q_plain, q_lat, k_cache, table)
+    T, ldx, n_parts, part_stride = _parts_of(x)
+    assert q_plain.is_contiguous() and q_lat.is_contiguous() and q_plain.dtype == q_lat.dtype
+    assert q_plain.shape == (T, n_heads, dim) and q_lat.shape == (T, n_heads, rank + rot)
+    assert c_weight.dtype == torch.float32 and c_weight.is_contiguous() and c_weight.numel() == rank
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    if cos is not None:
+        assert cos.dtype == torch.float32 and cos.is_contiguous() and cos.shape[1] == rotary_dim // 2 and sin.shape == cos.shape
+    _check(_lib("latent.cu").ub_latent_place(
+        _ptr(x), _code(x), ldx, n_parts, part_stride, int(q_off), int(c_off), _ptr(q_plain), _ptr(q_lat), _code(q_lat),
+        _ptr(c_weight), _ptr(cos), _ptr(sin), int(rotary_dim or 0), _ptr(tok_pos), _ptr(tok_seq), _ptr(k_cache), _code(k_cache),
+        _ptr(table), table.shape[1], ring, page, T, n_heads, dim, rot, rank, float(eps), _stream()), "latent_place")
+
+
+# ---------------------------------------------------------------------------------------
 # the state-space mixer (csrc/ssm.cu)
 def ssm_shape(H, P, N, G, taps, offs):
     """The shape record the state-space kernels read: sizes and the first columns of z, x, B, C and dt in a
@@ -515,11 +663,11 @@ def ssm_finish(y, p, shape, weight, out, n_groups, eps, scale=1.0):
 
 # ---------------------------------------------------------------------------------------
 # the gated delta-rule mixer (csrc/delta.cu)
-def delta_shape(H, G, D, E, taps, offs):
+def delta_shape(H, G, D, E, taps, offs, a_off=-1):
     """The shape record the delta kernels read: sizes and the first columns of q, k, v and the write
-    strength in a projection row."""
+    strength in a projection row; ``a_off`` >= 0: one decay a head, its sums in the row's columns from there on."""
     from ctypes import c_int as _ci
-    vals = [H, G, D, E, taps] + [int(o) for o in offs]
+    vals = [H, G, D, E, taps] + [int(o) for o in offs] + [int(a_off)]
     return (_ci * len(vals))(*vals)
 
 
@@ -541,7 +689,8 @@ def delta_prepare(p, shape, conv_w, conv_state, decay_pre, dt_bias, a_log, batch
     assert p.dtype == torch.float32
     T, ldp, n_parts, part_stride = _parts_of(p)
     for t in (conv_w, conv_state, decay_pre, dt_bias, a_log, qn, kn, vc, beta, dec):
-        assert t.dtype == torch.float32 and t.is_contiguous()
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    assert decay_pre is not None or shape[9] >= 0, "one decay a head reads its sums from the projection row"
     if update_state:
         assert batch.n_seqs == T, "the state moves on in this kernel only when every sequence brings one token"
     _check(_lib("delta.cu").ub_delta_prepare(
@@ -569,13 +718,16 @@ def delta_scan(qn, kn, vc, beta, dec, out, state, batch, H, G, D, E):
            "delta_scan")
 
 
-def delta_finish(o, gate_pre, weight, out, H, E, eps):
-    """out = o / rms(o) * weight * sigmoid(gate_pre), head by head; o, gate_pre float32 [T, H * E]."""
+def delta_finish(o, gate_pre, weight, out, H, E, eps, silu_gate=False):
+    """out = o / rms(o) * weight * sigmoid(gate_pre) (``silu_gate``: * silu(gate_pre)), head by head; o float32
+    [T, H * E]; gate_pre float32 [T, H * E] or [parts, T, H * E] (summed), rows of any stride."""
     _need_cuda(o, gate_pre, weight, out)
     assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
-    assert gate_pre.dtype == torch.float32 and gate_pre.is_contiguous() and gate_pre.shape == o.shape
-    _check(_lib("delta.cu").ub_delta_finish(_ptr(o), _ptr(gate_pre), _ptr(weight), _ptr(out), _code(out), o.shape[0], H, E,
-                                            float(eps), _stream()), "delta_finish")
+    assert gate_pre.dtype == torch.float32 and gate_pre.shape[-2:] == o.shape
+    _, ldz, n_parts, part_stride = _parts_of(gate_pre)
+    _check(_lib("delta.cu").ub_delta_finish(_ptr(o), _ptr(gate_pre), ldz, n_parts, part_stride, 1 if silu_gate else 0,
+                                            _ptr(weight), _ptr(out), _code(out), o.shape[0], H, E, float(eps), _stream()),
+           "delta_finish")
 
 
 # ---------------------------------------------------------------------------------------

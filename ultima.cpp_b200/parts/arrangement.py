@@ -233,3 +233,70 @@ class PassMarker(Entry):
     def forward(self, x, x0, rt):
         rt.launches += 1
         ops.add_rows(x, x0 if self.index > 0 else None, self.row)
+
+
+class _HyperPreNorm(Arrangement):
+    """A pre-norm layer over a residual stream kept in several copies (``ModelSpec.streams``): each sublayer reads
+    the copies through its connection and its norm, adds its result into a cleared float32 buffer y, and the
+    connection puts y into every copy (and clears it).  The mixer's write and the feed-forward's read are one pass
+    over the copies.  y is kept from layer to layer of a pass."""
+
+    def _buffer(self, xs, rt):
+        carry = getattr(rt, "_hyper_carry", None)
+        key = (rt.pass_id, xs.data_ptr(), tuple(xs.shape))
+        if carry is not None and carry[0] == key:
+            return carry[1]
+        y = rt.arena.alloc(tuple(xs.shape[1:]), xs.dtype)
+        y.zero_()
+        rt._hyper_carry = (key, y)
+        return y
+
+    def run(self, layer, xs, batch, cache, rt):
+        if xs.dim() != 3:
+            raise ValueError("this arrangement runs on a stream kept in copies (ModelSpec.streams > 0)")
+        y = self._buffer(xs, rt)
+        mark = rt.arena.mark()
+        h = layer.mixer_connection.read(xs, layer.mixer_norm, rt)
+        layer.mixer.forward(h, y, batch, cache, rt)
+        rt.arena.reset(mark)
+        ff = getattr(layer, "feed_forward", None)
+        if ff is None:
+            layer.mixer_connection.write(xs, y, rt)
+            return
+        h = layer.mixer_connection.write(xs, y, rt, then=(layer.feed_forward_connection, layer.feed_forward_norm))
+        ff.forward(h, y, batch, rt)
+        layer.feed_forward_connection.write(xs, y, rt)
+        rt.arena.reset(mark)
+
+
+@register_part("arrangement", "hyper_pre_norm")
+class HyperPreNorm(_HyperPreNorm):
+    roles = {"mixer_connection": "connection", "mixer_norm": "norm", "mixer": "mixer",
+             "feed_forward_connection": "connection", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
+    def __init__(self):
+        pass
+
+
+@register_part("arrangement", "hyper_pre_norm_mixer_only")
+class HyperPreNormMixerOnly(_HyperPreNorm):
+    """The same layer without a feed-forward."""
+    roles = {"mixer_connection": "connection", "mixer_norm": "norm", "mixer": "mixer"}
+
+    def __init__(self):
+        pass
+
+
+@register_part("arrangement", "pre_norm_mixer_only")
+class PreNormMixerOnly(Arrangement):
+    """x += mixer(norm(x)): the pre-norm block without a feed-forward."""
+    roles = {"mixer_norm": "norm", "mixer": "mixer"}
+
+    def __init__(self):
+        pass
+
+    def run(self, layer, x, batch, cache, rt):
+        mark = rt.arena.mark()
+        h = layer.mixer_norm.forward(x, rt)
+        layer.mixer.forward(h, x, batch, cache, rt)
+        rt.arena.reset(mark)

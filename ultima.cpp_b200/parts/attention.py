@@ -42,6 +42,11 @@ class Attention(Mixer):
       wide_gate   one more projection of the mixer's input, one number an output element; the heads' outputs
                   are multiplied by its sigmoid before the output projection
       out_scale   a constant on the mixer's output (applied to the heads' outputs, in float32)
+      softcap     c: a scaled score s becomes c * tanh(s / c)
+      distance_buckets   (B, D): a learned bias by distance, tensor ``rel`` [B, heads]; the key at distance n adds
+                  rel[bucket(n), h] to the score (behind scale and cap): bucket(n) = n below B // 2, beyond that
+                  min(B - 1, B // 2 + floor(ln(n / (B // 2)) / ln(D / (B // 2)) * (B - B // 2))), equal steps of ln(n) up to D
+      learned_sink   the sink's term is exp(sink[h]) with a learned number a head (tensor ``sink`` [heads]) instead of exp(0)
     With any of them the layer runs on the general kernels (csrc/attn_simple.cu: placement of q, k, v from
     one fused projection row [q | k | v | gate], attention with the mask and the gate inside); a block
     mask alone, with equal head sizes, still takes the tensor-core attention kernels.
@@ -58,7 +63,8 @@ class Attention(Mixer):
                  scale: float | None = None, v_head_dim: int | None = None, block: int | None = None,
                  head_gate: bool = False, own_kv: bool = True, norm_whole: bool = False, keep_first: int = 0,
                  distance_slope: float | None = None, sink: bool = False, values_are_keys: bool = False,
-                 wide_gate: bool = False, out_scale: float = 1.0):
+                 wide_gate: bool = False, out_scale: float = 1.0, softcap: float | None = None,
+                 distance_buckets: tuple | None = None, learned_sink: bool = False):
         if n_heads % n_kv_heads:
             raise ValueError("heads must be a multiple of kv heads")
         self.width, self.nh, self.nkv, self.hd = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
@@ -75,6 +81,16 @@ class Attention(Mixer):
         self.norm_whole, self.keep_first, self.sink = bool(norm_whole) and self.qk_norm, int(keep_first or 0), bool(sink)
         self.distance_slope = float(distance_slope) if distance_slope is not None else None
         self.values_are_keys, self.wide_gate, self.out_scale = bool(values_are_keys), bool(wide_gate), float(out_scale)
+        self.softcap = float(softcap) if softcap else None
+        self.distance_buckets = (int(distance_buckets[0]), float(distance_buckets[1])) if distance_buckets else None
+        self.learned_sink = bool(learned_sink)
+        if self.learned_sink:
+            self.sink = True
+        if self.distance_buckets is not None and (self.distance_buckets[0] < 2 or self.distance_buckets[1] <= self.distance_buckets[0] // 2):
+            raise ValueError("attention: a bias by distance needs at least two buckets and a largest distance beyond the "
+                             "buckets that hold one distance each")
+        if self.softcap is not None and self.softcap <= 0:
+            raise ValueError("attention: the score cap must be positive")
         if self.values_are_keys and (self.hdv != self.hd or not self.own_kv):
             raise ValueError("attention: values that are the keys have the keys' head size and belong to the layer itself")
         if self.wide_gate and self.head_gate:
@@ -86,7 +102,9 @@ class Attention(Mixer):
         # what only the row-wise placement and the any-shape attention kernel take
         interleaved = self.position is not None and bool(getattr(self.position, "interleaved", False))
         self.extended = (self.norm_whole or self.keep_first > 0 or self.distance_slope is not None or self.sink
-                         or self.values_are_keys or self.wide_gate or self.out_scale != 1.0)
+                         or self.values_are_keys or self.wide_gate or self.out_scale != 1.0 or self.softcap is not None
+                         or self.distance_buckets is not None)
+        self._table_options = self.softcap is not None or self.distance_buckets is not None or self.learned_sink
         self.place_rows = self.norm_whole or self.values_are_keys or self.wide_gate or (self.extended and interleaved)
         self.general = (self.hdv != self.hd or self.block is not None or self.head_gate or not self.own_kv
                         or self.extended)
@@ -109,6 +127,10 @@ class Attention(Mixer):
             s.append(WeightSpec("gate_proj.weight", (self.nh, self.width)))
         if self.wide_gate:
             s.append(WeightSpec("gate_proj.weight", (self.o_width, self.width)))
+        if self.distance_buckets is not None:
+            s.append(WeightSpec("rel", (self.distance_buckets[0], self.nh), "vector", ("normal", 0.5)))
+        if self.learned_sink:
+            s.append(WeightSpec("sink", (self.nh,), "vector", ("normal", 1.0)))
         return s
 
     def cache_need(self):
@@ -147,7 +169,7 @@ class Attention(Mixer):
     def _fast_extended(self) -> bool:
         """Whether a layer with the further options can go to the tensor-core kernels that know them (mma.sync):
         equal head sizes of a kind they take, no block mask, no gate a head."""
-        return (self.extended and self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256
+        return (self.extended and not self._table_options and self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256
                 and self.block is None and not self.head_gate and self.own_kv)
 
     def bind(self, tensors, rt):
@@ -176,6 +198,19 @@ class Attention(Mixer):
                                  "position encoding must be a rotation of pairs")
             if self.general and self.position.rotation().interleaved and not self.place_rows:
                 raise ValueError("attention: the head-wise placement kernel rotates pairs (j, j + rotary_dim / 2) only")
+        self.sink_vals = tensors["sink"].float().contiguous() if self.learned_sink else None
+        self.dist_bias = None
+        if self.distance_buckets is not None:
+            # the table by distance itself: row n is the bucket's row of ``rel``; beyond D every distance has the last bucket
+            B, D = self.distance_buckets
+            half = B // 2
+            reach = int(math.ceil(D)) + 1
+            if self.window:
+                reach = min(reach, int(self.window))
+            bucket = [n if n < half else min(B - 1, half + int(math.floor(math.log(n / half) / math.log(D / half) * (B - half))))
+                      for n in range(reach)]
+            rel = tensors["rel"].float()
+            self.dist_bias = rel[torch.tensor(bucket, dtype=torch.long, device=rel.device)].contiguous()
         self.slopes = self.slopes_log2 = None
         if self.distance_slope is not None:
             h = torch.arange(1, self.nh + 1, dtype=torch.float64)
@@ -234,7 +269,8 @@ class Attention(Mixer):
             rt.launches += 1
             ops.attn_simple(q, kv.k, kv.v, o, batch.tok_pos, batch.tok_seq, kv.table, kv.ring, kv.page, self.nh,
                             self.nkv, self.hd, self.window, self.scale, v_head_dim=self.hdv, block=self.block, gate=gate,
-                            keep_first=self.keep_first, slopes=self.slopes, sink=self.sink, out_scale=self.out_scale)
+                            keep_first=self.keep_first, slopes=self.slopes, sink=self.sink, out_scale=self.out_scale,
+                            softcap=self.softcap, dist_bias=self.dist_bias, sink_vals=self.sink_vals)
         rt.matmul(o, self.wo, residual, ops.EPI_ADD)
 
     def forward(self, h, residual, batch, cache, rt, projected=None):

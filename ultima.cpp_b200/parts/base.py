@@ -35,7 +35,8 @@ def part(kind: str, **params) -> PartSpec:
     return PartSpec(kind, tuple(sorted(params.items())))
 
 
-FAMILIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "residual_gate", "entry")
+FAMILIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "residual_gate", "entry",
+            "connection")
 _TABLES: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
 
 
@@ -71,11 +72,13 @@ def build_part(family: str, spec: PartSpec):
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values for every position (``window`` None) or for the last ``window``.
-    ``v_head_dim``: the values' head size where it is not the keys'."""
+    ``v_head_dim``: the values' head size where it is not the keys'.  ``values_in_keys``: the values are
+    columns of the key rows; no value pages are kept (the view's ``v`` is its ``k``)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)
@@ -187,6 +190,21 @@ class ResidualGate(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """How a sublayer meets a residual stream that is kept in several copies (``ModelSpec.streams``): what it reads
+    of them and how its result goes back into each."""
+    graph_safe = True
+
+    def read(self, xs, norm, rt):
+        """xs: float32 [streams, T, width] -> the sublayer's input (activations [T, width]), through ``norm``."""
+        raise NotImplementedError
+
+    def write(self, xs, y, rt, then=None):
+        """Put the sublayer's result y (float32 [T, width]) into the copies and clear y.  ``then`` = (connection, norm):
+        also return what that next sublayer reads (one pass over the copies instead of two)."""
+        raise NotImplementedError
+
+
 class Entry(Part):
     """What happens to the residual stream right before a run of the run list (``Run.entry``): a model
     that runs some of its layers several times may mark each pass this way."""
@@ -280,6 +298,9 @@ class ModelSpec:
     renames: tuple = ()
     # ((PartSpec of the family "entry", tensor-name prefix), ...): see ``Run.entry``
     entries: tuple = ()
+    # > 0: the residual stream is kept in this many copies [streams, T, width], all equal to the embedding's output at
+    # the start and summed before the final norm; the layers' arrangements then take the copies (family "connection")
+    streams: int = 0
 
     def stored_name(self, name: str) -> str:
         """The name under which the file holds the tensor a part calls ``name`` (prefix included)."""

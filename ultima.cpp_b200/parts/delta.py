@@ -29,17 +29,29 @@ class GatedDelta(Mixer):
     K slices that the next kernel adds up) and [decay_down | gate_down] in the activation type, which
     the two up-projections then take as their input (each padded to a multiple of 8 columns with zero
     weights, so that both are aligned operands of the tensor-core product).
+
+    Two further forms, each a parameter:
+      decay="head"   one decay a head instead of one a head and key channel:
+                     a = exp(-exp(a_log[h]) * softplus(a_proj h + dt_bias[h])), ``a_proj`` a matrix of ``heads`` rows
+      gate="silu"    the output gate is silu(gate_proj h) with a full matrix of heads * value size rows instead of
+                     the sigmoid of a low-rank product
+    Their rows join the one input product [q | k | v | b | a | gate], whose float32 sums the kernels read.
     """
 
     graph_safe = True
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int, conv: int,
-                 decay_rank: int, gate_rank: int, eps: float, unit_eps: float = 1e-6):
+                 decay_rank: int | None = None, gate_rank: int | None = None, eps: float = 1e-6, unit_eps: float = 1e-6,
+                 decay: str = "channel", gate: str = "sigmoid_lowrank"):
         if n_heads % n_kv_heads:
             raise ValueError("heads must be a multiple of kv heads")
         self.width, self.nh, self.nkv = int(width), int(n_heads), int(n_kv_heads)
         self.hd, self.hdv, self.conv = int(head_dim), int(v_head_dim), int(conv)
-        self.decay_rank, self.gate_rank = int(decay_rank), int(gate_rank)
+        if decay not in ("channel", "head") or gate not in ("sigmoid_lowrank", "silu"):
+            raise ValueError("gated_delta: decay is 'channel' or 'head', gate is 'sigmoid_lowrank' or 'silu'")
+        self.decay_per_head, self.gate_full = decay == "head", gate == "silu"
+        self.decay_rank = None if self.decay_per_head else int(decay_rank or 0)
+        self.gate_rank = None if self.gate_full else int(gate_rank or 0)
         self.eps, self.unit_eps = float(eps), float(unit_eps)
         self.qk_width, self.v_width = self.nkv * self.hd, self.nh * self.hdv
         self.channels = 2 * self.qk_width + self.v_width
@@ -47,23 +59,29 @@ class GatedDelta(Mixer):
             raise ValueError(f"gated_delta: a convolution of {self.conv} taps is not one the kernels take (1 to 16)")
         if self.hd > 256:
             raise ValueError(f"gated_delta: key size {self.hd} is more than the scan kernel holds (256)")
-        if self.decay_rank < 1 or self.gate_rank < 1:
+        if (self.decay_rank is not None and self.decay_rank < 1) or (self.gate_rank is not None and self.gate_rank < 1):
             raise ValueError("gated_delta: the low-rank products need inner sizes of at least 1")
 
     def weight_specs(self):
         W, V = WeightSpec, "vector"
-        return [W("q_proj.weight", (self.qk_width, self.width)), W("q_conv.weight", (self.qk_width, self.conv), V, ("normal", 0.3)),
-                W("k_proj.weight", (self.qk_width, self.width)), W("k_conv.weight", (self.qk_width, self.conv), V, ("normal", 0.3)),
-                W("v_proj.weight", (self.v_width, self.width)), W("v_conv.weight", (self.v_width, self.conv), V, ("normal", 0.3)),
-                W("b_proj.weight", (self.nh, self.width)),
-                W("a_log", (self.nh,), V, ("normal", 0.5)),
-                W("o_norm.weight", (self.hdv,), V, ("one_plus_normal", 0.05)),
-                W("decay_down.weight", (self.decay_rank, self.width)),
-                W("decay_up.weight", (self.nh * self.hd, self.decay_rank), "matrix", ("normal", 0.1)),
-                W("dt_bias", (self.nh * self.hd,), V, ("normal", 0.5)),
-                W("gate_down.weight", (self.gate_rank, self.width)),
-                W("gate_up.weight", (self.v_width, self.gate_rank), "matrix", ("normal", 0.1)),
-                W("o_proj.weight", (self.width, self.v_width))]
+        s = [W("q_proj.weight", (self.qk_width, self.width)), W("q_conv.weight", (self.qk_width, self.conv), V, ("normal", 0.3)),
+             W("k_proj.weight", (self.qk_width, self.width)), W("k_conv.weight", (self.qk_width, self.conv), V, ("normal", 0.3)),
+             W("v_proj.weight", (self.v_width, self.width)), W("v_conv.weight", (self.v_width, self.conv), V, ("normal", 0.3)),
+             W("b_proj.weight", (self.nh, self.width)),
+             W("a_log", (self.nh,), V, ("normal", 0.5)),
+             W("o_norm.weight", (self.hdv,), V, ("one_plus_normal", 0.05))]
+        if self.decay_per_head:
+            s += [W("a_proj.weight", (self.nh, self.width)), W("dt_bias", (self.nh,), V, ("normal", 0.5))]
+        else:
+            s += [W("decay_down.weight", (self.decay_rank, self.width)),
+                  W("decay_up.weight", (self.nh * self.hd, self.decay_rank), "matrix", ("normal", 0.1)),
+                  W("dt_bias", (self.nh * self.hd,), V, ("normal", 0.5))]
+        if self.gate_full:
+            s.append(W("gate_proj.weight", (self.v_width, self.width)))
+        else:
+            s += [W("gate_down.weight", (self.gate_rank, self.width)),
+                  W("gate_up.weight", (self.v_width, self.gate_rank), "matrix", ("normal", 0.1))]
+        return s + [W("o_proj.weight", (self.width, self.v_width))]
 
     def cache_need(self):
         taps = max(self.conv - 1, 1)
@@ -73,22 +91,33 @@ class GatedDelta(Mixer):
         return [("delta.cu", ())]
 
     def bind(self, tensors, rt):
-        ws = [tensors[n + ".weight"] for n in ("q_proj", "k_proj", "v_proj", "b_proj", "decay_down", "gate_down",
-                                               "decay_up", "gate_up")]
-        if len({w.dtype for w in ws}) != 1:
+        names = ["q_proj", "k_proj", "v_proj", "b_proj"] + (["a_proj"] if self.decay_per_head else []) \
+            + (["gate_proj"] if self.gate_full else [])
+        low = ([] if self.decay_per_head else ["decay_down"]) + ([] if self.gate_full else ["gate_down"])
+        ups = ([] if self.decay_per_head else ["decay_up"]) + ([] if self.gate_full else ["gate_up"])
+        ws = {n: tensors[n + ".weight"] for n in names + low + ups}
+        if len({w.dtype for w in ws.values()}) != 1:
             raise ValueError("gated_delta: the projections must share one element type")
-        self.w_in = torch.cat(ws[:4], dim=0).contiguous()
+        self.w_in = torch.cat([ws[n] for n in names], dim=0).contiguous()
         self.b_off = self.channels
+        self.a_off = self.b_off + self.nh if self.decay_per_head else -1
+        self.g_off = self.b_off + self.nh * (2 if self.decay_per_head else 1) if self.gate_full else -1
 
         def padded(w, rows, cols):
             out = torch.zeros((rows, cols), dtype=w.dtype, device=w.device)
             out[:w.shape[0], :w.shape[1]] = w
             return out
-        ra, rg = -(-self.decay_rank // 8) * 8, -(-self.gate_rank // 8) * 8
+        ra = 0 if self.decay_per_head else -(-self.decay_rank // 8) * 8
+        rg = 0 if self.gate_full else -(-self.gate_rank // 8) * 8
         self.low_split = ra
-        self.w_low = torch.cat([padded(ws[4], ra, self.width), padded(ws[5], rg, self.width)], dim=0).contiguous()
-        self.decay_up = padded(ws[6], ws[6].shape[0], ra).contiguous()
-        self.gate_up = padded(ws[7], ws[7].shape[0], rg).contiguous()
+        self.w_low = self.decay_up = self.gate_up = None
+        if low:
+            self.w_low = torch.cat([padded(ws[n], r, self.width) for n, r in (("decay_down", ra), ("gate_down", rg)) if n in ws],
+                                   dim=0).contiguous()
+        if not self.decay_per_head:
+            self.decay_up = padded(ws["decay_up"], ws["decay_up"].shape[0], ra).contiguous()
+        if not self.gate_full:
+            self.gate_up = padded(ws["gate_up"], ws["gate_up"].shape[0], rg).contiguous()
         self.conv_w = torch.cat([tensors[n].float() for n in ("q_conv.weight", "k_conv.weight", "v_conv.weight")],
                                 dim=0).contiguous()
         self.dt_bias = tensors["dt_bias"].float().contiguous()
@@ -96,7 +125,7 @@ class GatedDelta(Mixer):
         self.o_norm = tensors["o_norm.weight"].float().contiguous()
         self.wo = tensors["o_proj.weight"].contiguous()
         self.shape = ops.delta_shape(self.nh, self.nkv, self.hd, self.hdv, self.conv,
-                                     (0, self.qk_width, 2 * self.qk_width, self.b_off))
+                                     (0, self.qk_width, 2 * self.qk_width, self.b_off), a_off=self.a_off)
 
     def forward(self, h, residual, batch, cache, rt):
         T = h.shape[0]
@@ -106,12 +135,18 @@ class GatedDelta(Mixer):
         if p is None:
             p = rt.arena.alloc((T, self.w_in.shape[0]), f32)
             rt.matmul(h, self.w_in, p)
-        low = rt.arena.alloc((T, self.w_low.shape[0]), rt.dtype)
-        rt.matmul(h, self.w_low, low)
-        decay_pre = rt.arena.alloc((T, self.nh * self.hd), f32)
-        rt.matmul(low[:, :self.low_split], self.decay_up, decay_pre)
-        gate_pre = rt.arena.alloc((T, self.v_width), f32)
-        rt.matmul(low[:, self.low_split:], self.gate_up, gate_pre)
+        decay_pre = None
+        if self.w_low is not None:
+            low = rt.arena.alloc((T, self.w_low.shape[0]), rt.dtype)
+            rt.matmul(h, self.w_low, low)
+        if not self.decay_per_head:
+            decay_pre = rt.arena.alloc((T, self.nh * self.hd), f32)
+            rt.matmul(low[:, :self.low_split], self.decay_up, decay_pre)
+        if self.gate_full:
+            gate_pre = p[..., self.g_off:self.g_off + self.v_width]       # columns of the input product, summed by the kernel
+        else:
+            gate_pre = rt.arena.alloc((T, self.v_width), f32)
+            rt.matmul(low[:, self.low_split:], self.gate_up, gate_pre)
         qn = rt.arena.alloc((T, self.qk_width), f32)
         kn = rt.arena.alloc((T, self.qk_width), f32)
         vc = rt.arena.alloc((T, self.v_width), f32)
@@ -127,5 +162,5 @@ class GatedDelta(Mixer):
         if not one_each:
             ops.conv_state_update(p, conv_state, batch, self.channels, self.conv)
         ops.delta_scan(qn, kn, vc, beta, dec, o, S, batch, self.nh, self.nkv, self.hd, self.hdv)
-        ops.delta_finish(o, gate_pre, self.o_norm, oa, self.nh, self.hdv, self.eps)
+        ops.delta_finish(o, gate_pre, self.o_norm, oa, self.nh, self.hdv, self.eps, silu_gate=self.gate_full)
         rt.matmul(oa, self.wo, residual, ops.EPI_ADD)

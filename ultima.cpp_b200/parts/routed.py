@@ -1,0 +1,118 @@
+"""The routed feed-forward: a mixture of small gated feed-forwards of which a token uses a few."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..kernels import ops
+from ..weights.spec import WeightSpec
+from .base import FeedForward, build_part, part, register_part
+
+
+@dataclass
+class RoutePlan:
+    """Where a step's (token, choice) rows lie once they are sorted by expert, all on the device: ``tiles`` int32
+    [max_tiles, 4] (expert, first sorted row, rows, -), ``n_tiles`` int32 [1], ``src_rows`` int32 [rows]: the token
+    behind a sorted row.  ``gather``: the product reads its rows through ``src_rows`` (else they were copied)."""
+    tiles: torch.Tensor
+    n_tiles: torch.Tensor
+    src_rows: torch.Tensor
+    max_tiles: int
+    n_rows: int
+    gather: bool = True
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """``n_experts`` feed-forwards down(silu(gate h) * (up h)) of inner size ``inner`` (no biases), of which a token uses
+    ``top``.  The router: z = W_r h in float32 over n_experts + ``n_identity`` outputs, s = softmax(z); the choice
+    scores are s + correction (a stored vector); with ``groups`` = (count, keep) the outputs form ``count`` equal
+    groups of neighbours, a group's score is its largest choice score, and only outputs of the ``keep`` best groups can
+    be chosen (the others count as -inf); the ``top`` largest choice scores are chosen and weighted with their s, not
+    renormalised.  The last ``n_identity`` outputs are identity experts: they hand the input on (times the weight) and
+    have no tensors.  ``shared_inner``: one more gated feed-forward that every token uses, added unweighted.
+
+    On the GPU: the router's product on the CUDA cores with float32 weights; one kernel picks and counts, one lays
+    out the experts' segments and tiles, one hands every (token, choice) its sorted row; the experts' gate/up and
+    down products are two grouped products over the sorted rows (stacked weights [experts, 2 inner, width] and
+    [experts, width, inner]); one kernel adds the weighted rows into the stream in the order of the choices.  Nothing
+    is read on the host, so a step can be captured."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, n_experts: int, top: int, n_identity: int = 0, groups: tuple | None = None,
+                 shared_inner: int | None = None, correction: bool = True):
+        self.width, self.inner, self.ne, self.top = int(width), int(inner), int(n_experts), int(top)
+        self.ni = int(n_identity or 0)
+        self.n_out = self.ne + self.ni
+        self.groups = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+        self.correction = bool(correction)
+        if self.top > self.n_out or self.n_out % self.groups[0] or not (1 <= self.groups[1] <= self.groups[0]):
+            raise ValueError("routed_experts: top must not exceed the router's outputs, which divide into equal groups")
+        if self.n_out > 1024 or self.ne < 1:
+            raise ValueError("routed_experts: the router kernel takes up to 1,024 outputs, at least one of them an expert")
+        self.shared = build_part("feed_forward", part("gated_silu", width=self.width, inner=int(shared_inner))) \
+            if shared_inner else None
+
+    def weight_specs(self):
+        W = WeightSpec
+        s = [W("router.weight", (self.n_out, self.width), "matrix", ("normal", 0.3))]
+        if self.correction:
+            s.append(W("correction", (self.n_out,), "vector", ("normal", 0.05)))
+        for e in range(self.ne):
+            s += [W(f"experts.{e}.gate_proj.weight", (self.inner, self.width)),
+                  W(f"experts.{e}.up_proj.weight", (self.inner, self.width)),
+                  W(f"experts.{e}.down_proj.weight", (self.width, self.inner))]
+        if self.shared is not None:
+            s += [W("shared." + w.name, w.shape, w.kind, w.init) for w in self.shared.weight_specs()]
+        return s
+
+    def kernel_needs(self, run_dtype):
+        from ..kernels import gemm_mma
+        out = [("routed.cu", ())]
+        if run_dtype == torch.bfloat16:
+            out += gemm_mma.needs()
+        return out
+
+    def bind(self, tensors, rt):
+        self.w_router = tensors["router.weight"].float().contiguous()        # the router runs in 32-bit
+        self.corr = tensors["correction"].float().contiguous() if self.correction else None
+        g0 = tensors["experts.0.gate_proj.weight"]
+        self.w_gu = torch.empty((self.ne, 2 * self.inner, self.width), dtype=g0.dtype, device=g0.device)
+        self.w_down = torch.empty((self.ne, self.width, self.inner), dtype=g0.dtype, device=g0.device)
+        for e in range(self.ne):
+            self.w_gu[e, :self.inner] = tensors[f"experts.{e}.gate_proj.weight"]
+            self.w_gu[e, self.inner:] = tensors[f"experts.{e}.up_proj.weight"]
+            self.w_down[e] = tensors[f"experts.{e}.down_proj.weight"]
+        if self.shared is not None:
+            self.shared.bind({w.name: tensors["shared." + w.name] for w in self.shared.weight_specs()}, rt)
+        # counters of the routing kernels, shared by the model's routed layers (one runs at a time): rows of every
+        # expert, hand-out cursors, first sorted row of every expert, number of tiles
+        self.ws = rt.shared(("routed_counters", self.ne), lambda: torch.zeros(3 * self.ne + 4, dtype=torch.int32, device=rt.device))
+
+    def forward(self, h, residual, batch, rt):
+        T, ne, top = h.shape[0], self.ne, self.top
+        i32, f32 = torch.int32, torch.float32
+        z = rt.arena.alloc((T, self.n_out), f32)
+        rt.matmul(h, self.w_router, z)
+        idx = rt.arena.alloc((T, top), i32)
+        wts = rt.arena.alloc((T, top), f32)
+        row_pos = rt.arena.alloc((T, top), i32)
+        src_rows = rt.arena.alloc((T * top,), i32)
+        max_tiles = min(T * top, -(-T * top // ops.ROUTE_TILE) + ne)
+        tiles = rt.arena.alloc((max_tiles, 4), i32)
+        counts, cursor, seg_start, n_tiles = self.ws[:ne], self.ws[ne:2 * ne], self.ws[2 * ne:3 * ne], self.ws[3 * ne:3 * ne + 1]
+        rt.launches += 4
+        ops.route(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, counts)
+        ops.route_plan(counts, cursor, seg_start, tiles, n_tiles, ne)
+        ops.route_scatter(idx, seg_start, cursor, row_pos, src_rows, ne)
+        plan = RoutePlan(tiles, n_tiles, src_rows, max_tiles, T * top)
+        act = rt.arena.alloc((T * top, self.inner), rt.dtype)
+        rt.matmul_grouped(h, self.w_gu[:, :self.inner], act, plan, ops.EPI_SWIGLU, w2=self.w_gu[:, self.inner:])
+        y = rt.arena.alloc((T * top, self.width), f32)
+        plan.gather = False
+        rt.matmul_grouped(act, self.w_down, y, plan)
+        ops.route_combine(y, h, row_pos, wts, residual)
+        if self.shared is not None:
+            self.shared.forward(h, residual, batch, rt)
