@@ -489,6 +489,29 @@ def tinuzen_config(z):
             "loop": {"start": 0, "stop": z["layers"], "times": 1}, "layers": layers}
 
 
+def vusalix_config(z):
+    """Layers in fours: capped attention with a bias by distance and a sink, two delta-rule layers, latent attention; every
+    layer with a routed feed-forward whose active size (top experts and the shared one) is the dense models' ff; the
+    stream in two copies."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "softcap": 30.0, "bias_max": 2048, "buckets": 32, "mask": {"size": 1024}}
+    latent = {"heads": z["heads"], "dim": z["dim"], "rot_dim": 64, "vdim": z["dim"], "kv_rank": z.get("kv_rank", 512),
+              "scale": (z["dim"] + 64) ** -0.5, "mask": {"size": 1024},
+              "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    delta = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"] // 6}, "shared": {"ff": z["ff"] // 3},
+           "router": {"experts": 28, "identity": 4, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    kinds = ("attention", "delta", "delta", "latent_attention")
+    mixers = {"attention": att, "delta": delta, "latent_attention": latent}
+    layers = [{"type": kinds[i % 4], "mixer": dict(mixers[kinds[i % 4]]), "mlp": dict(mlp)} for i in range(z["layers"])]
+    return {"architecture": "Vusalix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "streams": 2,
+            "layers": layers}
+
+
+def vusalix_times(args):
+    return design_times(args, "vusalix", (("vusalix", vusalix_config), ("sugizen", sugizen_config), ("qwen3", qwen3_config_like)))
+
+
 def sugizen_times(args):
     return design_times(args, "sugizen", (("sugizen", sugizen_config), ("qwen3", qwen3_config_like)))
 
@@ -928,7 +951,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks", "sugizen", "tinuzen"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks", "sugizen", "tinuzen", "vusalix"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
                          "timeline: every kernel of a decode step with its begin and end inside the graph "
                          "(timeline-prefill: of a prompt); "
@@ -936,7 +959,8 @@ def main():
                          "peaks: this GPU's copy bandwidth and library bfloat16 product, the denominators' kind; "
                          "sugizen: prompt and decode throughput of the Sugizen design beside Qwen3 at equal layer sizes "
                          "(two widths, eight layers), with every kernel's time in a prompt and in a decode step; "
-                         "tinuzen: the same for the Tinuzen design beside Sugizen and Qwen3")
+                         "tinuzen: the same for the Tinuzen design beside Sugizen and Qwen3; "
+                         "vusalix: the same for the Vusalix design beside Sugizen and Qwen3")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
@@ -968,6 +992,8 @@ def main():
         return sugizen_times(args)
     if args.only == "tinuzen":
         return tinuzen_times(args)
+    if args.only == "vusalix":
+        return vusalix_times(args)
     if args.config != "8b":
         return run_other(args)
     return run_ours(args)

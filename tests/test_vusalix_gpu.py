@@ -127,6 +127,71 @@ def test_the_router_chooses_by_corrected_scores_within_the_kept_groups_and_weigh
 
 
 # ---------------------------------------------------------------------------------------
+# products of many small matrices on the tensor cores
+# ---------------------------------------------------------------------------------------
+class _Rt:
+    def __init__(self):
+        self.status = torch.zeros(4, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("tile", [16, 64, 128])
+def test_grouped_product_over_sorted_rows_on_the_tensor_cores(tile):
+    """Experts with no rows, with a few, with more than a tile and with exactly a tile; N no multiple of 128, K no
+    multiple of 64; the gate product from two halves of one stacked matrix, and the plain product into float32."""
+    from ultima_b200.kernels import gemm_tc
+    from ultima_b200.parts.routed import RoutePlan
+    ops = _ops()
+    counts = [0, 3, 130, tile, 17, 0, 1]
+    E, N, K = len(counts), 192, 136
+    rows = sum(counts)
+    g = torch.Generator().manual_seed(tile)
+    a = (torch.randn(rows + 5, K, generator=g)).to(torch.bfloat16).to(DEV)
+    a[rows:] = float("nan")                                     # rows of no expert: they must reach no result
+    w = (torch.randn(E, 2 * N, K, generator=g) * 0.2).to(torch.bfloat16).to(DEV)
+    max_tiles = -(-rows // tile) + E
+    tiles = torch.zeros(max_tiles + 3, 4, dtype=torch.int32, device=DEV)
+    ws = torch.zeros(3 * E + 1, dtype=torch.int32, device=DEV)
+    ws[:E] = torch.tensor(counts, dtype=torch.int32)
+    ops.route_plan(ws[:E], ws[E:2 * E], ws[2 * E:3 * E], tiles, ws[3 * E:], E, tile)
+    plan = RoutePlan(tiles, ws[3 * E:], None, max_tiles + 3, rows, gather=False, tile=tile)
+    expert = torch.repeat_interleave(torch.arange(E), torch.tensor(counts))
+    ad, wd = a[:rows].double().cpu(), w.double().cpu()
+    gate = torch.einsum("rk,rnk->rn", ad, wd[expert, :N])
+    up = torch.einsum("rk,rnk->rn", ad, wd[expert, N:])
+    rt = _Rt()
+    out = torch.full((rows + 5, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    assert gemm_tc.accepts_grouped(a, w[:, :N], out, ops.EPI_SWIGLU, w[:, N:])
+    gemm_tc.grouped(a, w[:, :N], out, plan, ops.EPI_SWIGLU, w[:, N:], rt)
+    assert rel_err(out[:rows], gate * torch.sigmoid(gate) * up) < 2 ** -7
+    assert bool((out[rows:] == 7.0).all()) and rt.status.tolist() == [0, 0, 0, 0]
+    out32 = torch.full((rows + 5, N), 7.0, device=DEV)
+    gemm_tc.grouped(a, w[:, N:], out32, plan, ops.EPI_STORE, None, rt)
+    assert rel_err(out32[:rows], up) < 1e-5 and bool((out32[rows:] == 7.0).all())
+    # against the CUDA-core product of the same rows
+    simt = torch.empty(rows, N, device=DEV)
+    ops.gemm_grouped(a, w[:, N:], simt, tiles, ws[3 * E:], None, max_tiles + 3)
+    assert rel_err(out32[:rows], simt) < 1e-5
+
+
+@pytest.mark.parametrize("T", [1, 37, 300])
+def test_one_small_matrix_a_head_on_the_tensor_cores(T):
+    """Inputs and outputs that are column ranges of wider rows, K no multiple of 64."""
+    from ultima_b200.kernels import gemm_tc
+    B, K, N = 3, 40, 72
+    g = torch.Generator().manual_seed(T)
+    wide_a = torch.randn(T, B, K + 24, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(B, N, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    a = wide_a[:, :, :K]
+    ref = torch.einsum("tbk,bnk->tbn", a.double().cpu(), w.double().cpu())
+    for dtype, tol in ((torch.bfloat16, 2 ** -7), (torch.float32, 1e-5)):
+        wide_o = torch.full((T, B, N + 8), 3.0, dtype=dtype, device=DEV)
+        out = wide_o[:, :, 8:]
+        assert gemm_tc.accepts_batched(a, w, out)
+        gemm_tc.batched(a, w, out, _Rt())
+        assert rel_err(out, ref) < tol and bool((wide_o[:, :, :8] == 3.0).all())
+
+
+# ---------------------------------------------------------------------------------------
 # models of one layer: every mixer and the routed feed-forward alone
 # ---------------------------------------------------------------------------------------
 def _model(layers, vocab=97, width=64, eps=1e-5, streams=None):

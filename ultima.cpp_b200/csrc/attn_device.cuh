@@ -118,12 +118,22 @@ __device__ __forceinline__ void weighted_values(float (*o)[4], const float (*s)[
 
 // One step of the running softmax over the masked scores of NT key groups; scores come in raw
 // (q.k) and leave as probabilities relative to the new maximum.  c = scale * log2(e).
+// What a score passes through before the softmax where a layer asks for it: raw = s * scale; with cap > 0
+// raw = cap * tanh(raw / cap); with a table, bias[min(distance, n_dist - 1) * nh + head] is added behind the cap.
+struct ScoreTable {
+    float cap, scale;
+    const float* bias;
+    int n_dist, nh;
+};
+
 // EXT: behind a window the sequence's first ``keep_first`` positions stay visible, and row r takes
-// row_slope[r] (a slope in units of log2) times its distance to the key off the score.
+// row_slope[r] (a slope in units of log2) times its distance to the key off the score.  ``tb`` (EXT only): the
+// score's cap and its bias by distance, for the heads ``row_head``.
 template <int NT, bool EXT = false>
 __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, float c,
                                              const int* row_pos, bool const* row_ok, int key_pos0, int window, int lane,
-                                             int keep_first = 0, const float* row_slope = nullptr) {
+                                             int keep_first = 0, const float* row_slope = nullptr,
+                                             const ScoreTable* tb = nullptr, const int* row_head = nullptr) {
     float mx[2] = {-INFINITY, -INFINITY};
     const int row_lo[2] = {span_lo(row_pos[0], window), span_lo(row_pos[1], window)};
 #pragma unroll
@@ -136,7 +146,15 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
             float v;
             if constexpr (EXT) {
                 ok = row_ok[r] && kp <= row_pos[r] && (kp >= row_lo[r] || kp < keep_first);
-                v = ok ? fmaf(-row_slope[r], (float)(row_pos[r] - kp), s[nt][e] * c) : -INFINITY;
+                if (tb) {
+                    float raw = s[nt][e] * tb->scale;
+                    if (tb->cap > 0.f) raw = tb->cap * tanhf(raw / tb->cap);
+                    const int d = row_pos[r] - kp;
+                    if (tb->bias && ok) raw += tb->bias[(long long)min(d, tb->n_dist - 1) * tb->nh + row_head[r]];
+                    v = ok ? fmaf(-row_slope[r], (float)d, raw * 1.4426950408889634f) : -INFINITY;
+                } else {
+                    v = ok ? fmaf(-row_slope[r], (float)(row_pos[r] - kp), s[nt][e] * c) : -INFINITY;
+                }
             } else {
                 v = ok ? s[nt][e] * c : -INFINITY;
             }

@@ -34,7 +34,16 @@ struct AttnParams {
     const float* slopes;
     float out_scale;
     const float* gate; long long g_stride;
+    // a cap on the scaled score (0: none), the plain scale, a bias by distance (float32 [n_dist, nh], added behind the
+    // cap; distances from n_dist - 1 on share the last row), and the sink's score a head (null: 0)
+    float softcap, scale;
+    const float* dist_bias; int n_dist;
+    const float* sink_vals;
 };
+
+__device__ __forceinline__ float sink_log2(const AttnParams& p, int head) {
+    return p.sink_vals ? p.sink_vals[head] * 1.4426950408889634f : 0.f;
+}
 
 // The tiles of 64 keys a query range reads, in order: with kept first positions, the tiles that hold them and lie
 // before the window's first tile, then the window's tiles t_lo .. t_hi.
@@ -97,9 +106,15 @@ attn_prefill_kernel(AttnParams p, PagedKV c) {
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float row_slope[2] = {0.f, 0.f};
     if constexpr (EXT) {
-        if (p.sink) { m[0] = m[1] = 0.f; l[0] = l[1] = 1.f; }         // the sink: a key with score 0 and no value
+        if (p.sink) {                                                  // the sink: a key with a score of its own and no value
+            m[0] = sink_log2(p, kvh * G + row_g[0]); m[1] = sink_log2(p, kvh * G + row_g[1]);
+            l[0] = l[1] = 1.f;
+        }
         if (p.slopes) { row_slope[0] = p.slopes[kvh * G + row_g[0]]; row_slope[1] = p.slopes[kvh * G + row_g[1]]; }
     }
+    const ScoreTable tb{p.softcap, p.scale, p.dist_bias, p.n_dist, p.nh};
+    const ScoreTable* tbp = (EXT && (p.softcap > 0.f || p.dist_bias)) ? &tb : nullptr;
+    const int row_head[2] = {kvh * G + row_g[0], kvh * G + row_g[1]};
     const TileList tiles(EXT ? p.keep_first : 0, t_lo, t_hi);
 
     load_kv_tile(Ks, Vs, p.kc, p.vc, c, seq, kvh, tiles.tile(0) * KT, last_pos, tid);
@@ -119,7 +134,7 @@ attn_prefill_kernel(AttnParams p, PagedKV c) {
         const bf16* V = Vs + buf * KT * LDS;
         float s[8][4];
         scores<8>(s, Qs, warp * 16, K, 0, lane);
-        softmax_step<8, EXT>(s, o, m, l, p.c, row_pos, row_ok, t * KT, p.window, lane, p.keep_first, row_slope);
+        softmax_step<8, EXT>(s, o, m, l, p.c, row_pos, row_ok, t * KT, p.window, lane, p.keep_first, row_slope, tbp, row_head);
         weighted_values<8>(o, s, V, 0, lane);
         __syncthreads();                             // the buffer is loaded again two tiles on
     }
@@ -184,6 +199,9 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
             if ((lane >> 2) + 8 < G) row_slope[1] = p.slopes[kvh * G + (lane >> 2) + 8];
         }
     }
+    const ScoreTable tb{p.softcap, p.scale, p.dist_bias, p.n_dist, p.nh};
+    const ScoreTable* tbp = (EXT && (p.softcap > 0.f || p.dist_bias)) ? &tb : nullptr;
+    const int row_head[2] = {kvh * G + min((lane >> 2), G - 1), kvh * G + min((lane >> 2) + 8, G - 1)};
 
     // a ring of DSTAGES tiles: DSTAGES - 1 tiles are on their way while one is used.  One group of
     // copies is committed for every tile slot, empty past the end, so the count to wait for is fixed.
@@ -205,7 +223,7 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
         __syncthreads();
         float s[2][4];
         scores<2>(s, Qs, 0, Ks + buf * KT * LDS, warp * 16, lane);
-        softmax_step<2, EXT>(s, o, m, l, p.c, row_pos, row_ok, tiles.tile(t) * KT + warp * 16, p.window, lane, p.keep_first, row_slope);
+        softmax_step<2, EXT>(s, o, m, l, p.c, row_pos, row_ok, tiles.tile(t) * KT + warp * 16, p.window, lane, p.keep_first, row_slope, tbp, row_head);
         weighted_values<2>(o, s, Vs + buf * KT * LDS, warp * 16, lane);
         __syncthreads();                             // the slot is filled again at the next step
     }
@@ -230,8 +248,9 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
 #pragma unroll
         for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[(w * 16 + g) * RS + HD]);
         const bool with_sink = EXT && p.sink && p.n_slices == 1;      // (with several slices the sink joins in attn_combine)
-        if (with_sink) mm = fmaxf(mm, 0.f);
-        float acc = 0.f, ll = with_sink ? exp2f(-mm) : 0.f;
+        const float sk = with_sink ? sink_log2(p, kvh * G + g) : 0.f;
+        if (with_sink) mm = fmaxf(mm, sk);
+        float acc = 0.f, ll = with_sink ? exp2f(sk - mm) : 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = red[(w * 16 + g) * RS + HD];
@@ -266,8 +285,9 @@ __global__ void attn_combine_kernel(AttnParams p) {
     float mm = -INFINITY;
     for (int s = 0; s < p.n_slices; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
     const bool with_sink = EXT && p.sink;
-    if (with_sink) mm = fmaxf(mm, 0.f);
-    float acc = 0.f, ll = with_sink ? exp2f(-mm) : 0.f;
+    const float sk = with_sink ? sink_log2(p, head) : 0.f;
+    if (with_sink) mm = fmaxf(mm, sk);
+    float acc = 0.f, ll = with_sink ? exp2f(sk - mm) : 0.f;
     for (int s = 0; s < p.n_slices; ++s) {
         const float ms = p.part_ml[(base + s) * 2];
         const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
@@ -333,6 +353,7 @@ static int fill_params(AttnParams& p, const void* q, long long q_stride, void* o
     p.nh = nh; p.group = nh / nkv; p.window = window; p.c = scale * 1.4426950408889634f;
     p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices;
     p.keep_first = 0; p.sink = 0; p.slopes = nullptr; p.out_scale = 1.0f; p.gate = nullptr; p.g_stride = 0;
+    p.softcap = 0.f; p.scale = scale; p.dist_bias = nullptr; p.n_dist = 0; p.sink_vals = nullptr;
     return 0;
 }
 
@@ -351,18 +372,23 @@ UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, l
 // The same two kernels with the further options: ``keep_first`` positions that stay visible behind the window
 // (window > 0), ``sink`` (one more term exp(0) in the softmax's sum), ``slopes`` (float32 [nh], already times
 // log2(e): slope * distance is taken off a score), ``out_scale``, and ``gate`` (float32 [tokens, nh * HD], row
-// stride g_stride: the output times its sigmoid, element by element).
+// stride g_stride: the output times its sigmoid, element by element), ``softcap`` (> 0: a scaled score s becomes
+// softcap * tanh(s / softcap)), ``dist_bias`` (float32 [n_dist, nh]: the row of min(distance, n_dist - 1) is added behind
+// the cap) and ``sink_vals`` (float32 [nh], with ``sink``: the sink's term is exp(sink_vals[h]) instead of exp(0)).
 UB_API int ub_attn_mma_ext(int mode, const void* q, long long q_stride, void* out, long long o_stride, const void* kcache,
                            const void* vcache, const int* seq_start, const int* seq_before, const int* table,
                            int pages_per_seq, int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window,
                            float scale, int n_slices, float* part_o, float* part_ml, int keep_first, int sink,
-                           const float* slopes, float out_scale, const float* gate, long long g_stride, cudaStream_t st) {
+                           const float* slopes, float out_scale, const float* gate, long long g_stride, float softcap,
+                           const float* dist_bias, int n_dist, const float* sink_vals, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (keep_first < 0 || window < 0 || (keep_first > 0 && window == 0)) return UB_ERR_ARG;
+    if (softcap < 0.f || (dist_bias && n_dist < 1) || (sink_vals && !sink)) return UB_ERR_ARG;
     AttnParams p;
     if (int rc = fill_params(p, q, q_stride, out, o_stride, kcache, vcache, seq_start, seq_before, ring, page, n_seqs, nh, nkv,
                              window, scale, n_slices, part_o, part_ml)) return rc;
     p.keep_first = keep_first; p.sink = sink ? 1 : 0; p.slopes = slopes; p.out_scale = out_scale; p.gate = gate; p.g_stride = g_stride;
+    p.softcap = softcap; p.dist_bias = dist_bias; p.n_dist = n_dist; p.sink_vals = sink_vals;
     PagedKV c{table, pages_per_seq, ring, page, nkv, HD};
     return launch_mma<true>(mode, p, c, n_seqs, max_new, nkv, st);
 }

@@ -263,6 +263,139 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------
+// Many small matrices in one launch: every tile of tokens meets the matrix its tile record names.
+//   grouped (``tiles`` given): tile y of the list int4 (matrix, first row, rows, -) made on the device; CTAs from
+//            ``*n_tiles`` on leave at once.  The rows are sorted by matrix (a routed feed-forward's experts).
+//   batched (``tiles`` null): blockIdx.z is the matrix, blockIdx.y the token tile; matrix b reads the columns
+//            from b * a_col_step on of the activation rows and writes the columns from b * o_col_step on (one small
+//            matrix a head).
+// Matrix e's rows lie from e * w_row_step on in the stacked weight map.  A tile's rows past its own count belong
+// to the next matrix (or to nobody); every output row depends on its own activation row only, and the epilogue
+// stores no row past the tile's count and no column past N, so what those rows hold never reaches a result.
+// Neither operand is fetched before the kernel in front has ended: the tile list is its output.
+// ---------------------------------------------------------------------------------------
+struct GroupParams {
+    const int4* tiles;
+    const int* n_tiles;
+    long long w_row_step;      // rows between two matrices in the weight map
+    int a_col_step;            // batched: columns between two matrices' inputs in an activation row
+    long long o_col_step;      // batched: columns between two matrices' outputs in an output row
+};
+
+template <int BN, int EPI, typename TO>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                       const __grid_constant__ CUtensorMap map_a, GemmParams p, GroupParams gp) {
+    using S = Smem<BN, EPI>;
+    extern __shared__ uint8_t smem_raw[];
+    pdl_wait();                                          // the tile list comes from the kernels before
+    int e, t0, t_end;
+    if (gp.tiles) {
+        if ((int)blockIdx.y >= *gp.n_tiles) return;
+        const int4 tl = gp.tiles[blockIdx.y];
+        e = tl.x; t0 = tl.y; t_end = tl.y + tl.z;
+    } else {
+        e = blockIdx.z; t0 = blockIdx.y * BN; t_end = p.T;
+    }
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + S::STAGES * S::STAGE_BYTES);
+    uint64_t* empty = full + S::STAGES;
+    uint64_t* acc_full = empty + S::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+    volatile int* err = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM;
+    const int w_row = (int)((long long)e * gp.w_row_step) + n0;
+    const int a_col = e * gp.a_col_step;
+    const int nkb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *err = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, S::TMEM_COLS); tmem_relinquish(); }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&map_w); prefetch_tmap(&map_a);
+        if (EPI == EPI_SWIGLU) prefetch_tmap(&map_w2);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int armed = 0;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S::STAGES;
+                const uint32_t ph = (i / S::STAGES) & 1;
+                if (i >= S::STAGES && !mbar_wait(&empty[s], ph ^ 1, err)) break;
+                uint8_t* st = smem + s * S::STAGE_BYTES;
+                mbar_expect_tx(&full[s], S::STAGE_BYTES);
+                const int kx = i * BK;
+                tma_load_2d(st, &map_w, &full[s], kx, w_row);
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + S::A_BYTES, &map_w2, &full[s], kx, w_row);
+                tma_load_2d(st + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1), &map_a, &full[s], a_col + kx, t0);
+                armed = i + 1;
+            }
+            if (*err) {
+                for (int i = max(0, armed - S::STAGES); i < armed; ++i) {
+                    const long long tstart = clock64();
+                    while (!mbar_try_wait(&full[i % S::STAGES], (i / S::STAGES) & 1))
+                        if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % S::STAGES;
+                const uint32_t ph = (i / S::STAGES) & 1;
+                ok = mbar_wait(&full[s], ph, err);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1);
+                const uint64_t da = make_desc(a_addr), db = make_desc(b_addr);
+                const uint64_t da2 = make_desc(a_addr + S::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+                    const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
+                    tc_mma_bf16(tmem_base, da + koff, db + koff, idesc, accum);
+                    if (EPI == EPI_SWIGLU) tc_mma_bf16(tmem_base + BN, da2 + koff, db + koff, idesc, accum);
+                }
+                tc_commit(&empty[s]);
+            }
+            tc_commit(acc_full);
+        }
+    } else {
+        const int q = warp & 3;
+        bool ok = nkb > 0 ? mbar_wait(acc_full, 0, err) : true;
+        tc_fence_after();
+        if (ok && nkb > 0) {
+            GemmParams pt = p;                           // this tile's rows end at t_end; matrix e's columns start at e * o_col_step
+            pt.T = t_end;
+            pt.out = (TO*)p.out + (long long)e * gp.o_col_step;
+            epilogue_tile<BN, EPI, TO>(pt, tmem_base, q, lane, blockIdx.x, t0, 0, (float*)smem);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *err) atomicExch(p.error, 1);
+}
+
+// ---------------------------------------------------------------------------------------
 // The same product for many tiles a CTA: one CTA an SM walks over tiles c, c + G, c + 2G, ...
 // The ring of stages never drains between tiles, and there are two accumulators in tensor
 // memory, so the epilogue of one tile runs while the MMAs of the next are issued.
@@ -744,6 +877,75 @@ UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, 
         case 64: return launch_bn<64>(mw, mw2, ma, p, epi, o_dtype, splits, st);
         case 128: return launch_bn<128>(mw, mw2, ma, p, epi, o_dtype, splits, st);
         case 256: return launch_bn<256>(mw, mw2, ma, p, epi, o_dtype, splits, st);
+    }
+    return UB_ERR_ARG;
+}
+
+// The grouped and the batched product (gemm_tc_grouped_kernel).  map_w (map_w2): the stacked matrices as one
+// [rows, K] matrix, boxes of 128 rows; map_a: the activation rows, boxes of ``bn`` rows.  Grouped: ``tiles`` and
+// ``n_tiles`` on the device, ``max_tiles`` the most the list can hold, tiles of at most ``bn`` rows.  Batched
+// (tiles null): ``n_mats`` matrices, T rows each.  Epilogues: store (bfloat16 or float32) and, with map_w2, the gate
+// product (bfloat16).
+template <int BN, int EPI, typename TO>
+static int launch_grouped(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma, const GemmParams& p,
+                          const GroupParams& gp, dim3 grid, cudaStream_t st) {
+    using S = Smem<BN, EPI>;
+    static bool attr_done = false;
+    auto kern = gemm_tc_grouped_kernel<BN, EPI, TO>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *mw, *mw2, *ma, p, gp);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+template <int BN>
+static int launch_grouped_bn(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma, const GemmParams& p,
+                             const GroupParams& gp, dim3 grid, int epi, int o_dtype, cudaStream_t st) {
+    if (epi == EPI_STORE && o_dtype == UB_BF16) return launch_grouped<BN, EPI_STORE, __nv_bfloat16>(mw, mw2, ma, p, gp, grid, st);
+    if (epi == EPI_STORE && o_dtype == UB_F32) return launch_grouped<BN, EPI_STORE, float>(mw, mw2, ma, p, gp, grid, st);
+    if (epi == EPI_SWIGLU && o_dtype == UB_BF16) return launch_grouped<BN, EPI_SWIGLU, __nv_bfloat16>(mw, mw2, ma, p, gp, grid, st);
+    return UB_ERR_UNSUPPORTED;
+}
+
+UB_API int ub_gemm_tc_grouped(const void* map_w, const void* map_w2, const void* map_a, void* out, int o_dtype, long long ldo,
+                              int T, int N, int K, int bn, int epi, const void* tiles, const int* n_tiles, int max_tiles,
+                              int n_mats, long long w_row_step, int a_col_step, long long o_col_step, int* error,
+                              cudaStream_t st) {
+    if (N <= 0 || (tiles ? max_tiles <= 0 : (T <= 0 || n_mats <= 0))) return 0;
+    if (K <= 0 || (tiles && !n_tiles) || (a_col_step % 8) != 0) return UB_ERR_ARG;
+    if (epi == EPI_SWIGLU && !map_w2) return UB_ERR_ARG;
+    GemmParams p;
+    p.out = out; p.ldo = ldo; p.split_stride = 0;
+    p.T = T; p.N = N; p.K = K;
+    p.kb_per_split = (K + BK - 1) / BK;
+    p.atomic = 0; p.share_tail = 0; p.error = error;
+    set_gate_constants(p, nullptr);
+    GroupParams gp;
+    gp.tiles = (const int4*)tiles; gp.n_tiles = n_tiles; gp.w_row_step = w_row_step; gp.a_col_step = a_col_step;
+    gp.o_col_step = o_col_step;
+    dim3 grid((N + BM - 1) / BM, tiles ? max_tiles : (T + bn - 1) / bn, tiles ? 1 : n_mats);
+    if (grid.y > 65535 || grid.z > 65535) return UB_ERR_ARG;
+    const CUtensorMap* mw = (const CUtensorMap*)map_w;
+    const CUtensorMap* mw2 = (const CUtensorMap*)(map_w2 ? map_w2 : map_w);
+    const CUtensorMap* ma = (const CUtensorMap*)map_a;
+    switch (bn) {
+        case 16: return launch_grouped_bn<16>(mw, mw2, ma, p, gp, grid, epi, o_dtype, st);
+        case 32: return launch_grouped_bn<32>(mw, mw2, ma, p, gp, grid, epi, o_dtype, st);
+        case 64: return launch_grouped_bn<64>(mw, mw2, ma, p, gp, grid, epi, o_dtype, st);
+        case 128: return launch_grouped_bn<128>(mw, mw2, ma, p, gp, grid, epi, o_dtype, st);
     }
     return UB_ERR_ARG;
 }

@@ -4,7 +4,7 @@
 // taken through its own W_uk once (q' = W_uk^T q_unrotated, ``rank`` numbers) so that q' . c = q_unrotated . (W_uk c),
 // the score is (q' . c + q_rotated . k_rotated) * scale over ONE shared key row of rank + rot numbers, the
 // weighted sum of the rows' leading ``rank`` numbers is taken through W_uv afterwards.  This file holds the
-// placement kernel; the two small products a head are batched products (gemm_simt.cu, gemm_mma.cu), the
+// placement kernel; the two small products a head are batched products (gemm_simt.cu; gemm_tcgen05.cu for bfloat16), the
 // attention itself is the ordinary attention over one key head whose value rows are the key rows.
 //
 // latent_place, one block a token, from a projection row x (the float32 sum of ``n_parts`` parts) that holds the

@@ -1,6 +1,6 @@
 // A routed feed-forward (mixture of experts): which experts a token uses, the order its rows are worked in,
 // and the weighted sum of what the experts return.  The experts' products themselves are grouped matrix
-// products over the sorted rows (gemm_simt.cu, gemm_mma.cu).
+// products over the sorted rows (gemm_simt.cu; gemm_tcgen05.cu for bfloat16).
 //
 //   route     one warp a token: s = softmax(z) over all router outputs (float32); choice scores s + correction;
 //             with groups, only the outputs of the ``keep`` groups with the largest choice score stay (the
@@ -12,6 +12,8 @@
 //             the counters for the next use.
 //   scatter   one thread a (token, choice): its place in its expert's segment (``row_pos``; -1 for an identity
 //             expert) and, for that place, the token it is (``src_rows``).
+//   gather    one block a (token, choice): the token's input row is copied to its sorted place, for a grouped
+//             product that reads its rows in the sorted order (the tensor-core one: a tile is one TMA box).
 //   combine   one block a token: residual += sum_k w_k * (expert row k, or the token's own input for an
 //             identity expert), in the order of k.
 // Places within a segment are handed out by an atomic counter, so they differ from run to run; every row of a
@@ -132,6 +134,17 @@ __global__ void scatter_kernel(const int* __restrict__ idx, const int* __restric
     src_rows[p] = (int)(i / top);
 }
 
+__global__ void gather_kernel(const uint4* __restrict__ h, const int* __restrict__ row_pos, uint4* __restrict__ sorted,
+                              int top, int row_vecs) {
+    pdl_trigger();
+    pdl_wait();
+    const int p = row_pos[blockIdx.x];
+    if (p < 0) return;
+    const uint4* src = h + (long long)(blockIdx.x / top) * row_vecs;
+    uint4* dst = sorted + (long long)p * row_vecs;
+    for (int c = threadIdx.x; c < row_vecs; c += blockDim.x) dst[c] = src[c];
+}
+
 template <typename TH, typename TY>
 __global__ void combine_kernel(const TY* __restrict__ y, const TH* __restrict__ h, const int* __restrict__ row_pos,
                                const float* __restrict__ wts, float* __restrict__ residual, int width, int top) {
@@ -193,4 +206,15 @@ UB_API int ub_route_combine(const void* y, int y_dtype, const void* h, int h_dty
     else return UB_ERR_UNSUPPORTED;
 #undef GO
     return (int)e;
+}
+
+// sorted[row_pos[t * top + k]] = h[t] for every choice with a row; rows of ``row_bytes`` bytes (a multiple of 16, both
+// buffers 16-byte aligned).
+UB_API int ub_route_gather(const void* h, const int* row_pos, void* sorted, int n_tokens, int top, long long row_bytes,
+                           cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (top < 1 || row_bytes < 16 || (row_bytes % 16) || ((uintptr_t)h & 15) || ((uintptr_t)sorted & 15)) return UB_ERR_ARG;
+    const int vecs = (int)(row_bytes / 16);
+    return (int)ub_launch_dependent(gather_kernel, dim3((unsigned)(n_tokens * top)), dim3(vecs < 256 ? ((vecs + 31) / 32) * 32 : 256),
+                                    0, st, (const uint4*)h, row_pos, (uint4*)sorted, top, vecs);
 }

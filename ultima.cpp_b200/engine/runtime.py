@@ -149,22 +149,29 @@ class Runtime:
         """out[:, b, :] = a[:, b, :] @ w[b].T for every b (one small matrix a head): a [T, B, K], w [B, N, K], out
         [T, B, N]; a and out may be column ranges of wider rows."""
         self.launches += 1
-        if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
-            from ..kernels import gemm_mma
-            if gemm_mma.accepts_batched(a, w, out):
-                return gemm_mma.batched(a, w, out)
+        if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            from ..kernels import gemm_tc
+            if gemm_tc.accepts_batched(a, w, out):
+                return gemm_tc.batched(a, w, out, self)
         return ops.gemm_batched(a, w, out)
 
     def matmul_grouped(self, a, w, out, plan, epilogue=ops.EPI_STORE, w2=None):
         """Sorted rows against the matrix their tile names (``plan``: a routed feed-forward's ``RoutePlan``):
-        out[p] = a[plan.src_rows[p] or p] @ w[e].T, e the expert of the tile that holds sorted row p."""
+        out[p] = a[plan.src_rows[p] or p] @ w[e].T, e the expert of the tile that holds sorted row p.  The tensor-core
+        product takes rows that lie in the sorted order already (``plan.gather`` False); ``grouped_on_tensor_cores``
+        says beforehand whether it will take a product."""
         self.launches += 1
-        if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-            from ..kernels import gemm_mma
-            if gemm_mma.accepts_grouped(a, w, out, epilogue):
-                return gemm_mma.grouped(a, w, out, plan, epilogue, w2)
+        if not plan.gather and self.grouped_on_tensor_cores(a, w, out, epilogue, w2):
+            from ..kernels import gemm_tc
+            return gemm_tc.grouped(a, w, out, plan, epilogue, w2, self)
         return ops.gemm_grouped(a, w, out, plan.tiles, plan.n_tiles, plan.src_rows if plan.gather else None, plan.max_tiles,
                                 epilogue, w2)
+
+    def grouped_on_tensor_cores(self, a, w, out, epilogue=ops.EPI_STORE, w2=None) -> bool:
+        if not (self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+            return False
+        from ..kernels import gemm_tc
+        return gemm_tc.accepts_grouped(a, w, out, epilogue, w2)
 
     # ---- attention ----------------------------------------------------------------------
     def attention_latent(self, q_lat, kv, batch, n_heads, row, rank, scale, window):

@@ -29,7 +29,8 @@ def lib(head_dim: int):
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_float, c_int, c_void_p, c_void_p, c_void_p]
         L.ub_attn_mma.restype = c_int
-        L.ub_attn_mma_ext.argtypes = L.ub_attn_mma.argtypes[:-1] + [c_int, c_int, c_void_p, c_float, c_void_p, c_longlong, c_void_p]
+        L.ub_attn_mma_ext.argtypes = L.ub_attn_mma.argtypes[:-1] + [c_int, c_int, c_void_p, c_float, c_void_p, c_longlong, c_float, c_void_p,
+                                                                       c_int, c_void_p, c_void_p]
         L.ub_attn_mma_ext.restype = c_int
         L.ub_attn_head_dim.restype = c_int
         if L.ub_attn_head_dim() != head_dim:
@@ -272,18 +273,26 @@ def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slice
 
 
 def attention_ext(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, window=None, keep_first=0, sink=False,
-                  slopes_log2=None, out_scale=1.0, gate=None, slices: int | None = None):
+                  slopes_log2=None, out_scale=1.0, gate=None, slices: int | None = None, softcap=None, dist_bias=None,
+                  sink_vals=None):
     """The mma.sync kernels (prompts, and single tokens with groups of up to 16 heads) with the further options of
     the attention part: ``window`` with ``keep_first`` positions kept visible behind it, ``sink``, ``slopes_log2``
     (float32 [heads], slope * log2(e)), ``out_scale`` and ``gate`` (float32 [T, heads * head size], contiguous: one
-    sigmoid gate an output element).  The cache holds every position or is a ring of the window's size."""
+    sigmoid gate an output element), ``softcap`` (a scaled score s becomes softcap * tanh(s / softcap)), ``dist_bias``
+    (float32 [distances, heads]: the row of min(distance, rows - 1) is added behind the cap) and ``sink_vals`` (float32
+    [heads]: the sink's term is exp(sink_vals[h])).  The cache holds every position or is a ring of the window's size."""
+    tabled = softcap is not None or dist_bias is not None or sink_vals is not None
+    if dist_bias is not None:
+        assert dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[1] == n_heads
+    if sink_vals is not None:
+        assert sink and sink_vals.dtype == torch.float32 and sink_vals.is_contiguous() and sink_vals.numel() == n_heads
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     group = n_heads // n_kv_heads
     decode = batch.max_new == 1 and group <= 16
     if gate is not None:
         assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (q.shape[0], n_heads * head_dim)
     # prompts without a window and without a bias by distance: the tcgen05 kernels know the sink, the scale and the gate
-    if (not decode and not window and not keep_first and slopes_log2 is None and tcgen05_fits(head_dim, n_heads, n_kv_heads)
+    if (not tabled and not decode and not window and not keep_first and slopes_log2 is None and tcgen05_fits(head_dim, n_heads, n_kv_heads)
             and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and kv.k.is_contiguous() and kv.v.is_contiguous()
             and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 4 == 0))):
         L = tc_lib(head_dim)
@@ -312,5 +321,6 @@ def attention_ext(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, w
                            _ptr(batch.seq_start), _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring,
                            kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, int(window or 0), float(scale),
                            n_slices, _ptr(part_o), _ptr(part_ml), int(keep_first or 0), 1 if sink else 0, _ptr(slopes_log2),
-                           float(out_scale), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+                           float(out_scale), _ptr(gate), gate.stride(0) if gate is not None else 0, float(softcap or 0.0),
+                           _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0, _ptr(sink_vals), _stream())
     _check(rc, "attn_mma_ext")

@@ -29,6 +29,10 @@ def lib():
         L.ub_gemm_tc_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
                                       c_void_p, c_void_p, c_void_p]
         L.ub_gemm_tc_pair.restype = c_int
+        L.ub_gemm_tc_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                                         c_int, c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_longlong, c_void_p,
+                                         c_void_p]
+        L.ub_gemm_tc_grouped.restype = c_int
         L.ub_gemm_tc_set_pdl.argtypes = [c_int]
         L.ub_gemm_tc_set_pdl.restype = None
         import os
@@ -215,3 +219,75 @@ def store_splits(T: int, N: int, K: int, n_sms: int | None = None) -> int:
 
 def check_error(rt) -> None:
     rt.check_status()
+
+
+# ---------------------------------------------------------------------------------------
+# many small matrices in one launch (gemm_tc_grouped_kernel)
+# ---------------------------------------------------------------------------------------
+GROUPED = os.environ.get("ULTIMA_GEMM_GROUPED", "1") != "0"      # 0: these products stay on the CUDA cores (for measurements)
+
+
+def _stacked(w: torch.Tensor):
+    """(2-D view of everything from the first matrix's first row to the last matrix's last row, rows between two
+    matrices) of stacked matrices w [E, N, K], or None when the stack is not one the tensor map can describe."""
+    E, N, K = w.shape
+    if w.dtype != torch.bfloat16 or w.stride(2) != 1 or w.stride(1) < K or w.stride(1) % 8 or w.data_ptr() % 16:
+        return None
+    if E > 1 and (w.stride(0) % w.stride(1) or w.stride(0) < N * w.stride(1)):
+        return None
+    step = w.stride(0) // w.stride(1) if E > 1 else N
+    return torch.as_strided(w, ((E - 1) * step + N, K), (w.stride(1), 1)), step
+
+
+def row_tile(rows: int, n_mats: int) -> int:
+    """Rows a tile of the grouped product for ``rows`` sorted rows over ``n_mats`` matrices: as many as a matrix gets
+    on average, between 16 and 128."""
+    avg = rows / max(1, n_mats)
+    return 128 if avg > 64 else 64 if avg > 32 else 32 if avg > 16 else 16
+
+
+def accepts_grouped(a, w, out, epilogue, w2=None) -> bool:
+    if not GROUPED or not _ok_operand(a) or a.shape[1] % 8 or w.dim() != 3 or _stacked(w) is None:
+        return False
+    if out.stride(1) != 1:
+        return False
+    if epilogue == EPI_SWIGLU:
+        return (w2 is not None and out.dtype == torch.bfloat16 and w2.shape == w.shape and w2.stride() == w.stride()
+                and _stacked(w2) is not None)
+    return epilogue == EPI_STORE and out.dtype in (torch.bfloat16, torch.float32)
+
+
+def grouped(a, w, out, plan, epilogue, w2, rt):
+    """out[p] = a[p] @ w[e].T for the sorted rows p of every tile (e, first row, rows) of ``plan``; a [rows, K] lies in
+    the sorted order already.  ``plan.tile`` is the most rows a tile has (16 to 128)."""
+    E, N, K = w.shape
+    wv, step = _stacked(w)
+    m2 = _tmap(_stacked(w2)[0], 128) if w2 is not None else 0
+    bn = int(plan.tile)
+    rc = lib().ub_gemm_tc_grouped(_tmap(wv, 128), m2, _tmap(a, bn), _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
+                                  out.stride(0), a.shape[0], N, K, bn, epilogue, _ptr(plan.tiles), _ptr(plan.n_tiles),
+                                  int(plan.max_tiles), E, step, 0, 0, _ptr(rt.status[1:2]), _stream())
+    _check(rc, "gemm_tc_grouped")
+
+
+def accepts_batched(a, w, out) -> bool:
+    if not GROUPED or a.dim() != 3 or w.dim() != 3 or not w.is_contiguous() or _stacked(w) is None:
+        return False
+    T, B, K = a.shape
+    return (a.dtype == torch.bfloat16 and a.stride(2) == 1 and out.stride(2) == 1 and K % 8 == 0 and a.stride(1) % 8 == 0
+            and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and a.stride(0) >= (B - 1) * a.stride(1) + K
+            and out.dtype in (torch.bfloat16, torch.float32))
+
+
+def batched(a, w, out, rt):
+    """out[:, b, :] = a[:, b, :] @ w[b].T: a [T, B, K] and out [T, B, N] may be column ranges of wider rows."""
+    T, B, K = a.shape
+    N = w.shape[1]
+    wv, step = _stacked(w)
+    a2 = torch.as_strided(a, (T, (B - 1) * a.stride(1) + K), (a.stride(0), 1))
+    bn = token_tile(T, EPI_STORE)
+    bn = min(bn, 128)
+    rc = lib().ub_gemm_tc_grouped(_tmap(wv, 128), 0, _tmap(a2, bn), _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
+                                  out.stride(0), T, N, K, bn, EPI_STORE, None, None, 0, B, step, a.stride(1), out.stride(1),
+                                  _ptr(rt.status[1:2]), _stream())
+    _check(rc, "gemm_tc_batched")

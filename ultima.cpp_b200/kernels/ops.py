@@ -122,7 +122,8 @@ def _declare(lib, source: str) -> None:
         "routed.cu": {"ub_route": [P, L, P, I, I, I, I, I, I, P, P, P, P],
                       "ub_route_plan": [P, P, P, P, P, I, I, P],
                       "ub_route_scatter": [P, P, P, P, P, I, I, I, P],
-                      "ub_route_combine": [P, I, P, I, P, P, P, I, I, I, P]},
+                      "ub_route_combine": [P, I, P, I, P, P, P, I, I, I, P],
+                      "ub_route_gather": [P, P, P, I, I, L, P]},
         "latent.cu": {"ub_latent_place": [P, I, L, I, L, I, I, P, P, I, P, P, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P]},
         "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, I, P, I, I, F, F, P, I, P, I, P],
                            "ub_qkv_place_rows": [P, I, L, I, L, I, I, I, P, I, L, P, P, I, P, P, I, I, P, P, P, P, I, P, I, I, I, I, I,
@@ -574,6 +575,16 @@ def route_scatter(idx, seg_start, cursor, row_pos, src_rows, n_experts):
     assert row_pos.dtype == src_rows.dtype == torch.int32 and row_pos.numel() == T * top and src_rows.numel() >= T * top
     _check(_lib("routed.cu").ub_route_scatter(_ptr(idx), _ptr(seg_start), _ptr(cursor), _ptr(row_pos), _ptr(src_rows), T, top,
                                               n_experts, _stream()), "route_scatter")
+
+
+def route_gather(h, row_pos, out):
+    """out[row_pos[t, k]] = h[t] for every choice that has a row (row_pos >= 0): the tokens' rows in the sorted order."""
+    _need_cuda(h, row_pos, out)
+    T, top = row_pos.shape
+    assert h.is_contiguous() and out.is_contiguous() and h.dtype == out.dtype and h.shape[0] == T and out.shape[1] == h.shape[1]
+    assert row_pos.dtype == torch.int32 and row_pos.is_contiguous()
+    _check(_lib("routed.cu").ub_route_gather(_ptr(h), _ptr(row_pos), _ptr(out), T, top, h.shape[1] * h.element_size(), _stream()),
+           "route_gather")
 
 
 def route_combine(y, h, row_pos, wts, residual):

@@ -169,7 +169,7 @@ class Attention(Mixer):
     def _fast_extended(self) -> bool:
         """Whether a layer with the further options can go to the tensor-core kernels that know them (mma.sync):
         equal head sizes of a kind they take, no block mask, no gate a head."""
-        return (self.extended and not self._table_options and self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256
+        return (self.extended and self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256
                 and self.block is None and not self.head_gate and self.own_kv)
 
     def bind(self, tensors, rt):
@@ -258,7 +258,8 @@ class Attention(Mixer):
         o = rt.arena.alloc((T, self.o_width), rt.dtype)
         if self._fast_extended() and rt.attention_ext(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale, window=self.window,
                                                       keep_first=self.keep_first, sink=self.sink, slopes_log2=self.slopes_log2,
-                                                      out_scale=self.out_scale, gate=gate):
+                                                      out_scale=self.out_scale, gate=gate, softcap=self.softcap,
+                                                      dist_bias=self.dist_bias, sink_vals=self.sink_vals):
             pass
         elif self._fast_attention() and rt.attention_fast(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale,
                                                           self.block):

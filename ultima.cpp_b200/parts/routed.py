@@ -21,6 +21,7 @@ class RoutePlan:
     max_tiles: int
     n_rows: int
     gather: bool = True
+    tile: int = ops.ROUTE_TILE           # the most rows a tile has
 
 
 @register_part("feed_forward", "routed_experts")
@@ -36,8 +37,11 @@ class RoutedExperts(FeedForward):
     On the GPU: the router's product on the CUDA cores with float32 weights; one kernel picks and counts, one lays
     out the experts' segments and tiles, one hands every (token, choice) its sorted row; the experts' gate/up and
     down products are two grouped products over the sorted rows (stacked weights [experts, 2 inner, width] and
-    [experts, width, inner]); one kernel adds the weighted rows into the stream in the order of the choices.  Nothing
-    is read on the host, so a step can be captured."""
+    [experts, width, inner]); one kernel adds the weighted rows into the stream in the order of the choices.  In
+    bfloat16 the grouped products run on the tensor cores (tcgen05, tiles of 16 to 128 rows by the rows an expert
+    gets on average), for which one more kernel copies the tokens' rows into the sorted order; in float32, and with
+    sizes the tensor maps do not take, on the CUDA cores, which read the rows through the list.  Nothing is read on
+    the host, so a step can be captured."""
 
     graph_safe = True
 
@@ -69,10 +73,9 @@ class RoutedExperts(FeedForward):
         return s
 
     def kernel_needs(self, run_dtype):
-        from ..kernels import gemm_mma
         out = [("routed.cu", ())]
         if run_dtype == torch.bfloat16:
-            out += gemm_mma.needs()
+            out.append(("gemm_tcgen05.cu", ()))
         return out
 
     def bind(self, tensors, rt):
@@ -100,19 +103,35 @@ class RoutedExperts(FeedForward):
         wts = rt.arena.alloc((T, top), f32)
         row_pos = rt.arena.alloc((T, top), i32)
         src_rows = rt.arena.alloc((T * top,), i32)
-        max_tiles = min(T * top, -(-T * top // ops.ROUTE_TILE) + ne)
+        act = rt.arena.alloc((T * top, self.inner), rt.dtype)
+        y = rt.arena.alloc((T * top, self.width), f32)
+        w_gate, w_up = self.w_gu[:, :self.inner], self.w_gu[:, self.inner:]
+        # the tensor-core products take both or neither: their tiles are cut to the rows an expert gets on average
+        fast = (rt.grouped_on_tensor_cores(h, w_gate, act, ops.EPI_SWIGLU, w_up)
+                and rt.grouped_on_tensor_cores(act, self.w_down, y))
+        tile = ops.ROUTE_TILE
+        if fast:
+            from ..kernels import gemm_tc
+            tile = gemm_tc.row_tile(T * top, ne)
+        max_tiles = min(T * top, -(-T * top // tile) + ne)
         tiles = rt.arena.alloc((max_tiles, 4), i32)
         counts, cursor, seg_start, n_tiles = self.ws[:ne], self.ws[ne:2 * ne], self.ws[2 * ne:3 * ne], self.ws[3 * ne:3 * ne + 1]
-        rt.launches += 4
+        rt.launches += 3
         ops.route(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, counts)
-        ops.route_plan(counts, cursor, seg_start, tiles, n_tiles, ne)
+        ops.route_plan(counts, cursor, seg_start, tiles, n_tiles, ne, tile)
         ops.route_scatter(idx, seg_start, cursor, row_pos, src_rows, ne)
-        plan = RoutePlan(tiles, n_tiles, src_rows, max_tiles, T * top)
-        act = rt.arena.alloc((T * top, self.inner), rt.dtype)
-        rt.matmul_grouped(h, self.w_gu[:, :self.inner], act, plan, ops.EPI_SWIGLU, w2=self.w_gu[:, self.inner:])
-        y = rt.arena.alloc((T * top, self.width), f32)
+        plan = RoutePlan(tiles, n_tiles, src_rows, max_tiles, T * top, tile=tile)
+        if fast:
+            rows = rt.arena.alloc((T * top, self.width), rt.dtype)
+            rt.launches += 1
+            ops.route_gather(h, row_pos, rows)
+            plan.gather = False
+            rt.matmul_grouped(rows, w_gate, act, plan, ops.EPI_SWIGLU, w2=w_up)
+        else:
+            rt.matmul_grouped(h, w_gate, act, plan, ops.EPI_SWIGLU, w2=w_up)
         plan.gather = False
         rt.matmul_grouped(act, self.w_down, y, plan)
+        rt.launches += 1
         ops.route_combine(y, h, row_pos, wts, residual)
         if self.shared is not None:
             self.shared.forward(h, residual, batch, rt)
