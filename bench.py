@@ -492,10 +492,11 @@ def tinuzen_config(z):
 def vusalix_config(z):
     """Layers in fours: capped attention with a bias by distance and a sink, two delta-rule layers, latent attention; every
     layer with a routed feed-forward whose active size (top experts and the shared one) is the dense models' ff; the
-    stream in two copies."""
+    stream in two copies.  The latent layers keep 192 + 64 numbers a position: a key row of 256, the widest the
+    tensor-core attention kernels take (wider rows run on the any-shape kernel)."""
     att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
            "softcap": 30.0, "bias_max": 2048, "buckets": 32, "mask": {"size": 1024}}
-    latent = {"heads": z["heads"], "dim": z["dim"], "rot_dim": 64, "vdim": z["dim"], "kv_rank": z.get("kv_rank", 512),
+    latent = {"heads": z["heads"], "dim": z["dim"], "rot_dim": 64, "vdim": z["dim"], "kv_rank": z.get("kv_rank", 192),
               "scale": (z["dim"] + 64) ** -0.5, "mask": {"size": 1024},
               "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     delta = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4}

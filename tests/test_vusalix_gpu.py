@@ -167,10 +167,10 @@ def test_grouped_product_over_sorted_rows_on_the_tensor_cores(tile):
     out32 = torch.full((rows + 5, N), 7.0, device=DEV)
     gemm_tc.grouped(a, w[:, N:], out32, plan, ops.EPI_STORE, None, rt)
     assert rel_err(out32[:rows], up) < 1e-5 and bool((out32[rows:] == 7.0).all())
-    # against the CUDA-core product of the same rows
-    simt = torch.empty(rows, N, device=DEV)
-    ops.gemm_grouped(a, w[:, N:], simt, tiles, ws[3 * E:], None, max_tiles + 3)
-    assert rel_err(out32[:rows], simt) < 1e-5
+    if tile <= ops.ROUTE_TILE:                                  # against the CUDA-core product of the same tiles
+        simt = torch.empty(rows, N, device=DEV)
+        ops.gemm_grouped(a, w[:, N:], simt, tiles, ws[3 * E:], None, max_tiles + 3)
+        assert rel_err(out32[:rows], simt) < 1e-5
 
 
 @pytest.mark.parametrize("T", [1, 37, 300])
@@ -243,8 +243,17 @@ def folders(tmp_path_factory):
 
     def get(name, raw=None, change=None):
         if name not in made:
-            d = str(base / name)
-            u.write_random_model(d, u.config_from_dict(raw or CONFIGS.get(name) or ONE_LAYER[name]), seed=len(name), dtype="bfloat16")
+            d = str(base / name.replace("/", "_"))
+            plain_name = name.split("/")[0]
+            raw = copy.deepcopy(raw or CONFIGS.get(plain_name) or ONE_LAYER[plain_name])
+            if name.endswith("/all_chosen"):
+                for L in raw["layers"]:
+                    if L.get("mlp"):
+                        r = L["mlp"]["router"]
+                        r["top"] = r["experts"] + r.get("identity", 0)
+                        if r.get("groups"):
+                            r["groups"]["keep"] = r["groups"]["count"]
+            u.write_random_model(d, u.config_from_dict(raw), seed=len(plain_name), dtype="bfloat16")
             cfg, W = P.read_folder(d)
             W = _sharpen(W)
             if change is not None:
@@ -264,6 +273,15 @@ def _engine(folder, dtype, **kw):
     if key not in _engines:
         _engines[key] = Engine.from_dir(folder, dtype=dtype, with_sampler=False, **{"max_tokens": 2048, "max_seqs": 6, **kw})
     return _engines[key]
+
+
+def _for(name, dtype):
+    """The model's folder for a run in ``dtype``.  In bfloat16 a router's close call between two outputs may go either
+    way, and one other choice reaches every later position through states and keys; so the bfloat16 runs of whole
+    models use the same models with routers that choose every output (the weights still differ from token to token).
+    The choice itself is held to the plain implementation by the 32-bit runs of the same models, by the one-layer
+    models in both types and by the router's own test."""
+    return name + "/all_chosen" if dtype == "bfloat16" else name
 
 
 def _whole(eng, ids, want=None):
@@ -421,7 +439,7 @@ def test_the_sink_takes_weight_and_the_state_keeps_an_early_input(folders):
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_a_prompt_in_one_step_every_position_and_every_layer(folders, name, dtype):
     import plain_vusalix as P
-    d, cfg, W = folders(name)
+    d, cfg, W = folders(_for(name, dtype))
     eng = _engine(d, dtype, poison_cache=True)
     L = len(cfg["layers"])
     for seed, n in ((1, 1), (2, 2), (3, 277)):                 # 277: past window and page borders of every configuration
@@ -468,7 +486,7 @@ def test_prompt_against_token_by_token_and_portions(folders, name):
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_unequal_requests_together_then_decoded_with_slots_used_again(folders, name, dtype):
     import plain_vusalix as P
-    d, cfg, W = folders(name)
+    d, cfg, W = folders(_for(name, dtype))
     eng = _engine(d, dtype, poison_cache=True)
     L = len(cfg["layers"])
     for round_ in range(2):                                    # the second time on slots and pages just given back
@@ -502,7 +520,7 @@ def test_unequal_requests_together_then_decoded_with_slots_used_again(folders, n
 @pytest.mark.parametrize("name", ["mixed", "plain"])
 def test_long_decoding_over_window_and_page_borders(folders, name, dtype):
     import plain_vusalix as P
-    d, cfg, W = folders(name)
+    d, cfg, W = folders(_for(name, dtype))
     eng = _engine(d, dtype)
     ids = _ids(5, 210, cfg["vocab"])
     ref = P.logits(cfg, W, ids)
@@ -537,6 +555,7 @@ def test_trace_replay_and_the_command_line(folders, tmp_path):
                       "end": ["a", "b"] if t == 3 else []})
     steps.append({"step": 5, "entries": [{"id": "c", "tokens": b, "want": [8]}], "end": ["c"]})      # a slot used again
     for dtype in ("float32", "bfloat16"):
+        d, cfg, W = folders(_for("odd", dtype))
         out_dir = str(tmp_path / ("out_" + dtype))
         p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
                             "--out", out_dir, "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps),

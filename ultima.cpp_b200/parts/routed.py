@@ -34,7 +34,8 @@ class RoutedExperts(FeedForward):
     renormalised.  The last ``n_identity`` outputs are identity experts: they hand the input on (times the weight) and
     have no tensors.  ``shared_inner``: one more gated feed-forward that every token uses, added unweighted.
 
-    On the GPU: the router's product on the CUDA cores with float32 weights; one kernel picks and counts, one lays
+    On the GPU: the router's product with float32 sums (CUDA cores and float32 weights; in a bfloat16 run the stored
+    bfloat16 weights on the tensor cores, whose products of two bfloat16 numbers are exact); one kernel picks and counts, one lays
     out the experts' segments and tiles, one hands every (token, choice) its sorted row; the experts' gate/up and
     down products are two grouped products over the sorted rows (stacked weights [experts, 2 inner, width] and
     [experts, width, inner]); one kernel adds the weighted rows into the stream in the order of the choices.  In
@@ -79,7 +80,12 @@ class RoutedExperts(FeedForward):
         return out
 
     def bind(self, tensors, rt):
-        self.w_router = tensors["router.weight"].float().contiguous()        # the router runs in 32-bit
+        # the router's sums are 32-bit.  Stored bfloat16 weights against the bfloat16 rounding of the input give exact
+        # products, so that pair may go to the tensor cores, which add them up in float32; anything else runs on the
+        # CUDA cores with float32 weights
+        wr = tensors["router.weight"]
+        self.w_router = wr.contiguous() if (wr.dtype == torch.bfloat16 and rt.dtype == torch.bfloat16 and self.width % 8 == 0) \
+            else wr.float().contiguous()
         self.corr = tensors["correction"].float().contiguous() if self.correction else None
         g0 = tensors["experts.0.gate_proj.weight"]
         self.w_gu = torch.empty((self.ne, 2 * self.inner, self.width), dtype=g0.dtype, device=g0.device)
