@@ -61,7 +61,8 @@ def agree(got, ref, dtype, layers, what):
 # the copies of the stream
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,T,width", [(1, 5, 48), (2, 37, 100), (3, 64, 64), (5, 130, 257), (8, 3, 1024)])
+@pytest.mark.parametrize("S,T,width", [(1, 5, 48), (2, 37, 100), (3, 64, 64), (5, 130, 257), (8, 3, 1024), (4, 9, 2048), (2, 3, 4100),
+                                       (3, 7, 130)])
 def test_a_pass_over_the_copies_writes_and_reads(S, T, width, out_dtype):
     ops = _ops()
     g = torch.Generator().manual_seed(S * 100 + T)
@@ -98,7 +99,7 @@ def test_a_pass_over_the_copies_writes_and_reads(S, T, width, out_dtype):
 # ---------------------------------------------------------------------------------------
 # the router
 # ---------------------------------------------------------------------------------------
-@pytest.mark.parametrize("ne,ni,groups,top", [(6, 2, (4, 2), 3), (16, 4, (2, 1), 4), (5, 0, None, 2), (3, 1, None, 1),
+@pytest.mark.parametrize("ne,ni,groups,top", [(6, 2, (4, 2), 3), (20, 4, (2, 1), 5), (5, 0, None, 2), (3, 1, None, 1),
                                               (12, 4, (4, 3), 3), (8, 0, (8, 2), 2), (60, 4, (8, 3), 6)])
 def test_the_router_chooses_by_corrected_scores_within_the_kept_groups_and_weights_by_the_plain_ones(ne, ni, groups, top):
     """The correction is larger than the scores and partly negative, so that choice scores are negative too: an
@@ -124,6 +125,40 @@ def test_the_router_chooses_by_corrected_scores_within_the_kept_groups_and_weigh
         assert set(got) == set(want), (t, got, want)
         assert all(abs(got[e] - want[e]) < 1e-6 for e in want), (t, got, want)
     assert counts.cpu().tolist() == torch.bincount(ref_idx[ref_idx < ne].flatten(), minlength=ne).tolist()
+    # the same logits handed over as three K slices whose sum they are
+    coarse = (z * 4).round() / 4
+    rest = z - coarse
+    parts = torch.stack([coarse, rest, torch.zeros_like(z)]).contiguous()        # (both sums are exact)
+    assert torch.equal(parts[0] + parts[1] + parts[2], z)
+    idx2, wts2 = torch.empty_like(idx, dtype=torch.int32, device=DEV), torch.empty(T, top, device=DEV)
+    counts.zero_()
+    ops.route(parts.to(DEV), corr.to(DEV), ne, top, groups[0] if groups else 1, groups[1] if groups else 1, idx2, wts2, counts)
+    assert torch.equal(idx2.cpu().long(), idx) and torch.equal(wts2.cpu().double(), wts)
+
+
+@pytest.mark.parametrize("y_dtype,h_dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                             (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("T,width,top", [(1, 30, 1), (7, 64, 3), (33, 100, 2), (5, 4104, 4), (3, 1030, 5)])
+def test_the_weighted_sum_of_the_chosen_rows_with_identity_choices(T, width, top, y_dtype, h_dtype):
+    """Widths that are and are not a multiple of 4 (four columns a thread, or one); a choice without a row hands the
+    token's own input on."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(T * 7 + top)
+    rows = T * top
+    y = torch.randn(rows + 2, width, generator=g).to(y_dtype)
+    h = torch.randn(T, width, generator=g).to(h_dtype)
+    res = torch.randn(T, width, generator=g)
+    wts = torch.rand(T, top, generator=g)
+    row_pos = torch.randperm(rows + 2, generator=g)[:rows].reshape(T, top).to(torch.int32)
+    row_pos[torch.rand(T, top, generator=g) < 0.3] = -1
+    want = res.double().clone()
+    for t in range(T):
+        for k in range(top):
+            src = h[t] if row_pos[t, k] < 0 else y[row_pos[t, k]]
+            want[t] += wts[t, k].double() * src.double()
+    out = res.to(DEV)
+    ops.route_combine(y.to(DEV), h.to(DEV), row_pos.to(DEV), wts.to(DEV), out)
+    assert rel_err(out, want) < 1e-6
 
 
 # ---------------------------------------------------------------------------------------

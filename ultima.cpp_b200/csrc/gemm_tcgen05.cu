@@ -65,13 +65,13 @@ static void set_gate_constants(GemmParams& p, const float* gate) {
     p.act_shift = gate ? gate[2] : 0.0f;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int KB = 0>
 struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1) + B_BYTES;
-    // token tiles of up to 64 leave room for two CTAs on an SM (this kernel's and the next one's)
-    static constexpr int BUDGET = (BN <= 64 && EPI != EPI_SWIGLU ? 110 : 196) * 1024;
+    // token tiles of up to 64 leave room for two CTAs on an SM (this kernel's and the next one's); KB: a budget given
+    static constexpr int BUDGET = (KB > 0 ? KB : (BN <= 64 && EPI != EPI_SWIGLU ? 110 : 196)) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     // (the interleaved gate product's exchange buffer, 4 KB, lies over the first stage: the epilogue runs when
@@ -274,6 +274,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // stores no row past the tile's count and no column past N, so what those rows hold never reaches a result.
 // Neither operand is fetched before the kernel in front has ended: the tile list is its output.
 // ---------------------------------------------------------------------------------------
+// Shared memory a CTA of the grouped product with tiles of 128 rows takes, in KB (0: the single product's rule).  A
+// tile of few k-blocks spends a good part of its time before and behind the main loop; with half an SM's shared memory
+// two CTAs live on an SM and one's epilogue runs beside the other's loads (measured: a prompt of 2,048 tokens 3 to 5 %
+// shorter than with one CTA and all of the shared memory).
+#ifndef GROUPED_KB
+#define GROUPED_KB 110
+#endif
 struct GroupParams {
     const int4* tiles;
     const int* n_tiles;
@@ -286,7 +293,7 @@ template <int BN, int EPI, typename TO>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                        const __grid_constant__ CUtensorMap map_a, GemmParams p, GroupParams gp) {
-    using S = Smem<BN, EPI>;
+    using S = Smem<BN, EPI, (BN >= 128 ? GROUPED_KB : 0)>;
     extern __shared__ uint8_t smem_raw[];
     pdl_wait();                                          // the tile list comes from the kernels before
     int e, t0, t_end;
@@ -889,7 +896,7 @@ UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, 
 template <int BN, int EPI, typename TO>
 static int launch_grouped(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma, const GemmParams& p,
                           const GroupParams& gp, dim3 grid, cudaStream_t st) {
-    using S = Smem<BN, EPI>;
+    using S = Smem<BN, EPI, (BN >= 128 ? GROUPED_KB : 0)>;
     static bool attr_done = false;
     auto kern = gemm_tc_grouped_kernel<BN, EPI, TO>;
     if (!attr_done) {

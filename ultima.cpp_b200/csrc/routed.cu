@@ -23,8 +23,9 @@
 constexpr int ROUTE_WARPS = 4;
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-route_kernel(const float* __restrict__ z, long long ldz, const float* __restrict__ corr, int n_tokens, int n_out, int n_experts,
-             int top, int n_groups, int keep, int* __restrict__ idx, float* __restrict__ wts, int* __restrict__ counts) {
+route_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long part_stride, const float* __restrict__ corr,
+             int n_tokens, int n_out, int n_experts, int top, int n_groups, int keep, int* __restrict__ idx,
+             float* __restrict__ wts, int* __restrict__ counts) {
     extern __shared__ float sm[];
     pdl_trigger();
     pdl_wait();
@@ -36,10 +37,15 @@ route_kernel(const float* __restrict__ z, long long ldz, const float* __restrict
     float* gm = ch + n_out;                                      // a group's best choice score
     const float* zr = z + t * ldz;
     float m = -INFINITY;
-    for (int i = lane; i < n_out; i += 32) m = fmaxf(m, zr[i]);
+    for (int i = lane; i < n_out; i += 32) {              // the logits may come as K slices: summed in the slices' order
+        float v = zr[i];
+        for (int s = 1; s < n_parts; ++s) v += zr[s * part_stride + i];
+        sc[i] = v;
+        m = fmaxf(m, v);
+    }
     m = warp_max(m);
     float sum = 0.f;
-    for (int i = lane; i < n_out; i += 32) { const float e = expf(zr[i] - m); sc[i] = e; sum += e; }
+    for (int i = lane; i < n_out; i += 32) { const float e = expf(sc[i] - m); sc[i] = e; sum += e; }
     sum = warp_sum(sum);
     for (int i = lane; i < n_out; i += 32) { const float s = sc[i] / sum; sc[i] = s; ch[i] = s + (corr ? corr[i] : 0.f); }
     __syncwarp();
@@ -162,16 +168,53 @@ __global__ void combine_kernel(const TY* __restrict__ y, const TH* __restrict__ 
     }
 }
 
-UB_API int ub_route(const float* z, long long ldz, const float* corr, int n_tokens, int n_out, int n_experts, int top,
-                    int n_groups, int keep, int* idx, float* wts, int* counts, cudaStream_t st) {
+// The same sum four columns a thread and a part of a row a block (width a multiple of 4, rows 16-byte aligned): a step
+// of few tokens still fills the SMs.  An element's sum has the order of the kernel above.
+template <typename T>
+__device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename TH, typename TY>
+__global__ void combine_vec_kernel(const TY* __restrict__ y, const TH* __restrict__ h, const int* __restrict__ row_pos,
+                                   const float* __restrict__ wts, float* __restrict__ residual, int width, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= width) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top; ++k) {
+        const int p = row_pos[t * top + k];
+        const float w = wts[t * top + k];
+        const float4 v = p >= 0 ? load4<TY>(y + (long long)p * width + c) : load4<TH>(h + t * width + c);
+        acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+    }
+    float4* r = reinterpret_cast<float4*>(residual + t * width + c);
+    float4 o = *r;
+    o.x += acc.x; o.y += acc.y; o.z += acc.z; o.w += acc.w;
+    *r = o;
+}
+
+// z: the router's logits [tokens, outputs] (row stride ldz), or ``n_parts`` such arrays ``part_stride`` floats apart
+// whose sum they are.
+UB_API int ub_route(const float* z, long long ldz, int n_parts, long long part_stride, const float* corr, int n_tokens,
+                    int n_out, int n_experts, int top, int n_groups, int keep, int* idx, float* wts, int* counts,
+                    cudaStream_t st) {
     if (n_tokens <= 0) return 0;
+    if (n_parts < 1) return UB_ERR_ARG;
     if (n_out < 1 || n_experts < 0 || n_experts > n_out || top < 1 || top > n_out || n_groups < 1 || n_out % n_groups ||
         keep < 1 || keep > n_groups) return UB_ERR_ARG;
     const size_t smem = (size_t)ROUTE_WARPS * (2 * n_out + n_groups) * sizeof(float);
     if (smem > 48 * 1024) return UB_ERR_ARG;
     const unsigned grid = (unsigned)((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS);
-    return (int)ub_launch_dependent(route_kernel, dim3(grid), dim3(ROUTE_WARPS * 32), smem, st, z, ldz, corr, n_tokens, n_out,
-                                    n_experts, top, n_groups, keep, idx, wts, counts);
+    return (int)ub_launch_dependent(route_kernel, dim3(grid), dim3(ROUTE_WARPS * 32), smem, st, z, ldz, n_parts, part_stride, corr,
+                                    n_tokens, n_out, n_experts, top, n_groups, keep, idx, wts, counts);
 }
 
 UB_API int ub_route_plan(int* counts, int* cursor, int* seg_start, void* tiles, int* n_tiles, int n_experts, int tile,
@@ -198,8 +241,13 @@ UB_API int ub_route_combine(const void* y, int y_dtype, const void* h, int h_dty
     if (n_tokens <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     cudaError_t e;
-#define GO(TH, TY) e = ub_launch_dependent(combine_kernel<TH, TY>, dim3(n_tokens), dim3(threads), 0, st, (const TY*)y, (const TH*)h, \
-                                           row_pos, wts, residual, width, top)
+    const bool vec = width % 4 == 0 && !(((uintptr_t)y | (uintptr_t)h | (uintptr_t)residual) & 15);
+    const int vthreads = 128;
+    const dim3 vgrid(n_tokens, (width / 4 + vthreads - 1) / vthreads);
+#define GO(TH, TY) e = vec ? ub_launch_dependent(combine_vec_kernel<TH, TY>, vgrid, dim3(vthreads), 0, st, (const TY*)y, (const TH*)h, \
+                                                 row_pos, wts, residual, width, top) \
+                           : ub_launch_dependent(combine_kernel<TH, TY>, dim3(n_tokens), dim3(threads), 0, st, (const TY*)y, (const TH*)h, \
+                                                 row_pos, wts, residual, width, top)
     if (h_dtype == UB_F32 && y_dtype == UB_F32) GO(float, float);
     else if (h_dtype == UB_BF16 && y_dtype == UB_F32) GO(__nv_bfloat16, float);
     else if (h_dtype == UB_BF16 && y_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16);

@@ -20,7 +20,10 @@ _maps: dict = {}
 def lib():
     global _lib
     if _lib is None:
-        L = build.load(SOURCE)
+        import os
+        # for measurements: -D switches of the source (ULTIMA_GEMM_DEFINES="GROUPED_KB=110,...")
+        extra = tuple(x for x in os.environ.get("ULTIMA_GEMM_DEFINES", "").split(",") if x)
+        L = build.load(SOURCE, extra)
         L.ub_tmap_bf16_2d.argtypes = [c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int]
         L.ub_tmap_bf16_2d.restype = c_int
         L.ub_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong,

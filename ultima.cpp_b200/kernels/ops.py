@@ -119,7 +119,7 @@ def _declare(lib, source: str) -> None:
                          "ub_gemm_simt_grouped": [P, I, P, P, I, P, I, I, I, L, L, L, L, P, P, P, I, I, P]},
         "streams.cu": {"ub_streams_fill": [P, P, I, I, I, P],
                        "ub_streams_pass": [P, L, I, P, P, P, P, I, P, P, P, I, I, I, F, P]},
-        "routed.cu": {"ub_route": [P, L, P, I, I, I, I, I, I, P, P, P, P],
+        "routed.cu": {"ub_route": [P, L, I, L, P, I, I, I, I, I, I, P, P, P, P],
                       "ub_route_plan": [P, P, P, P, P, I, I, P],
                       "ub_route_scatter": [P, P, P, P, P, I, I, I, P],
                       "ub_route_combine": [P, I, P, I, P, P, P, I, I, I, P],
@@ -551,13 +551,15 @@ ROUTE_TILE = 64          # sorted rows a tile of the grouped products
 
 
 def route(z, correction, n_experts, top, n_groups, keep, idx, wts, counts):
-    """z float32 [T, outputs] router logits -> idx int32 [T, top], wts float32 [T, top]; counts int32 [n_experts] += rows."""
+    """z float32 [T, outputs] router logits (or [parts, T, outputs], summed in that order) -> idx int32 [T, top], wts
+    float32 [T, top]; counts int32 [n_experts] += rows."""
     _need_cuda(z, correction, idx, wts, counts)
-    T, n_out = z.shape
-    assert z.dtype == torch.float32 and z.stride(1) == 1 and idx.dtype == torch.int32 and wts.dtype == torch.float32
+    T, ldz, n_parts, part_stride = _parts_of(z)
+    n_out = z.shape[-1]
+    assert z.dtype == torch.float32 and z.stride(-1) == 1 and idx.dtype == torch.int32 and wts.dtype == torch.float32
     assert idx.is_contiguous() and wts.is_contiguous() and idx.shape == wts.shape == (T, top) and counts.dtype == torch.int32
     assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == n_out)
-    _check(_lib("routed.cu").ub_route(_ptr(z), z.stride(0), _ptr(correction), T, n_out, n_experts, top, n_groups, keep,
+    _check(_lib("routed.cu").ub_route(_ptr(z), ldz, n_parts, part_stride, _ptr(correction), T, n_out, n_experts, top, n_groups, keep,
                                       _ptr(idx), _ptr(wts), _ptr(counts), _stream()), "route")
 
 

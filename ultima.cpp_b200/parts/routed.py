@@ -103,8 +103,10 @@ class RoutedExperts(FeedForward):
     def forward(self, h, residual, batch, rt):
         T, ne, top = h.shape[0], self.ne, self.top
         i32, f32 = torch.int32, torch.float32
-        z = rt.arena.alloc((T, self.n_out), f32)
-        rt.matmul(h, self.w_router, z)
+        z = rt.matmul_parts(h, self.w_router)          # few tokens: K in slices, summed by the routing kernel
+        if z is None:
+            z = rt.arena.alloc((T, self.n_out), f32)
+            rt.matmul(h, self.w_router, z)
         idx = rt.arena.alloc((T, top), i32)
         wts = rt.arena.alloc((T, top), f32)
         row_pos = rt.arena.alloc((T, top), i32)
