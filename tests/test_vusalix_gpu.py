@@ -242,6 +242,8 @@ ONE_LAYER = {
     "attention_capped": _model([_layer("attention", _attention(6, 2, 16, 24, 0.4, 50, 10, softcap=3.0, mask=45))]),
     "attention_no_cap_no_window": _model([_layer("attention", _attention(2, 2, 40, 8, 0.3, 300, 9))], width=72),
     "attention_one_head": _model([_layer("attention", _attention(1, 1, 64, 64, 0.2, 20, 4, softcap=50.0, mask=1))], streams=2),
+    # a table by distance too large for the prompt kernel's shared memory (8 heads a group, 901 distances): read in place
+    "attention_wide_table": _model([_layer("attention", _attention(8, 1, 16, 16, 0.3, 900, 24, softcap=6.0))]),
     "latent_rescaled": _model([_layer("latent_attention", _latent(3, 24, 16, 40, 48, 0.2, 500.0, _YARN, mask=33))]),
     "latent_plain": _model([_layer("latent_attention", _latent(5, 8, 4, 8, 12, 0.5, 10000.0))], width=40, streams=3),
     "delta_shared_keys": _model([_layer("delta", _delta(6, 2, 16, 24, 4))]),

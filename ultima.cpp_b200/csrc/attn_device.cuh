@@ -120,10 +120,19 @@ __device__ __forceinline__ void weighted_values(float (*o)[4], const float (*s)[
 // (q.k) and leave as probabilities relative to the new maximum.  c = scale * log2(e).
 // What a score passes through before the softmax where a layer asks for it: raw = s * scale; with cap > 0
 // raw = cap * tanh(raw / cap); with a table, bias[min(distance, n_dist - 1) * nh + head] is added behind the cap.
+// tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1) on the fast exponential and reciprocal: an absolute error of a few 1e-7, far
+// below what the bfloat16 operands of these kernels leave in a score, at a fifth of tanhf's instructions.
+__device__ __forceinline__ float tanh_ex2(float x) {
+    return 1.0f - __fdividef(2.0f, exp2f(x * 2.8853900817779268f) + 1.0f);
+}
+
+// The table's entry for distance d and a row's head index hi lies at bias[min(d, n_dist - 1) * d_stride + hi * h_stride]:
+// the table as it is in global memory ([n_dist, heads]: d_stride = heads, h_stride = 1, hi the head), or a CTA's copy of its
+// own heads' columns in shared memory ([heads of the group][h_stride]: d_stride = 1, hi the head within the group).
 struct ScoreTable {
     float cap, scale;
     const float* bias;
-    int n_dist, nh;
+    int n_dist, d_stride, h_stride;
 };
 
 // EXT: behind a window the sequence's first ``keep_first`` positions stay visible, and row r takes
@@ -136,6 +145,7 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
                                              const ScoreTable* tb = nullptr, const int* row_head = nullptr) {
     float mx[2] = {-INFINITY, -INFINITY};
     const int row_lo[2] = {span_lo(row_pos[0], window), span_lo(row_pos[1], window)};
+    const float cap = (EXT && tb) ? tb->cap : 0.f, inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -148,9 +158,9 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
                 ok = row_ok[r] && kp <= row_pos[r] && (kp >= row_lo[r] || kp < keep_first);
                 if (tb) {
                     float raw = s[nt][e] * tb->scale;
-                    if (tb->cap > 0.f) raw = tb->cap * tanhf(raw / tb->cap);
+                    if (cap > 0.f) raw = cap * tanh_ex2(raw * inv_cap);
                     const int d = row_pos[r] - kp;
-                    if (tb->bias && ok) raw += tb->bias[(long long)min(d, tb->n_dist - 1) * tb->nh + row_head[r]];
+                    if (tb->bias && ok) raw += tb->bias[min(d, tb->n_dist - 1) * tb->d_stride + row_head[r] * tb->h_stride];
                     v = ok ? fmaf(-row_slope[r], (float)d, raw * 1.4426950408889634f) : -INFINITY;
                 } else {
                     v = ok ? fmaf(-row_slope[r], (float)(row_pos[r] - kp), s[nt][e] * c) : -INFINITY;

@@ -39,7 +39,12 @@ struct AttnParams {
     float softcap, scale;
     const float* dist_bias; int n_dist;
     const float* sink_vals;
+    int bias_stride;                          // > 0: the prompt kernel keeps its heads' columns of the table in shared memory, this far apart
 };
+
+// Most shared memory the prompt kernel spends on its copy of the table by distance; a larger table is read from global memory.
+constexpr int BIAS_SMEM_MAX = 24 * 1024;
+__host__ __device__ inline int bias_stride_for(int n_dist) { return ((n_dist + 31) / 32) * 32 + 8; }   // heads 8 banks apart
 
 __device__ __forceinline__ float sink_log2(const AttnParams& p, int head) {
     return p.sink_vals ? p.sink_vals[head] * 1.4426950408889634f : 0.f;
@@ -112,9 +117,20 @@ attn_prefill_kernel(AttnParams p, PagedKV c) {
         }
         if (p.slopes) { row_slope[0] = p.slopes[kvh * G + row_g[0]]; row_slope[1] = p.slopes[kvh * G + row_g[1]]; }
     }
-    const ScoreTable tb{p.softcap, p.scale, p.dist_bias, p.n_dist, p.nh};
+    // the table by distance: this CTA's heads' columns go to shared memory where they fit (read before the first use
+    // behind the loop's first barrier)
+    const bool bias_here = EXT && p.dist_bias && p.bias_stride > 0;
+    if (bias_here) {
+        float* Bs = (float*)(Vs + 2 * KT * LDS);
+        for (int i = tid; i < G * p.n_dist; i += NTHREADS) {
+            const int d = i / G, g = i % G;
+            Bs[g * p.bias_stride + d] = p.dist_bias[(long long)d * p.nh + kvh * G + g];
+        }
+    }
+    const ScoreTable tb{p.softcap, p.scale, bias_here ? (const float*)(Vs + 2 * KT * LDS) : p.dist_bias, p.n_dist,
+                        bias_here ? 1 : p.nh, bias_here ? p.bias_stride : 1};
     const ScoreTable* tbp = (EXT && (p.softcap > 0.f || p.dist_bias)) ? &tb : nullptr;
-    const int row_head[2] = {kvh * G + row_g[0], kvh * G + row_g[1]};
+    const int row_head[2] = {bias_here ? row_g[0] : kvh * G + row_g[0], bias_here ? row_g[1] : kvh * G + row_g[1]};
     const TileList tiles(EXT ? p.keep_first : 0, t_lo, t_hi);
 
     load_kv_tile(Ks, Vs, p.kc, p.vc, c, seq, kvh, tiles.tile(0) * KT, last_pos, tid);
@@ -199,7 +215,7 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
             if ((lane >> 2) + 8 < G) row_slope[1] = p.slopes[kvh * G + (lane >> 2) + 8];
         }
     }
-    const ScoreTable tb{p.softcap, p.scale, p.dist_bias, p.n_dist, p.nh};
+    const ScoreTable tb{p.softcap, p.scale, p.dist_bias, p.n_dist, p.nh, 1};
     const ScoreTable* tbp = (EXT && (p.softcap > 0.f || p.dist_bias)) ? &tb : nullptr;
     const int row_head[2] = {kvh * G + min((lane >> 2), G - 1), kvh * G + min((lane >> 2) + 8, G - 1)};
 
@@ -312,11 +328,19 @@ UB_API int ub_attn_head_dim() { return HD; }
 template <bool EXT>
 static int launch_mma(int mode, AttnParams p, PagedKV c, int n_seqs, int max_new, int nkv, cudaStream_t st) {
     static bool attr_done = false;
-    const size_t sm_pre = (size_t)(64 + 4 * KT) * LDS * sizeof(bf16);
+    const size_t sm_pre_plain = (size_t)(64 + 4 * KT) * LDS * sizeof(bf16);
+    size_t sm_bias = 0;
+    p.bias_stride = 0;
+    if (EXT && mode == 0 && p.dist_bias) {
+        const size_t need = (size_t)p.group * bias_stride_for(p.n_dist) * sizeof(float);
+        if (need <= (size_t)BIAS_SMEM_MAX) { sm_bias = need; p.bias_stride = bias_stride_for(p.n_dist); }
+    }
+    const size_t sm_pre = sm_pre_plain + sm_bias;
     const size_t sm_kv = (size_t)2 * DSTAGES * KT * LDS * sizeof(bf16), sm_red = (size_t)64 * (HD + 2) * sizeof(float);
     const size_t sm_dec = (size_t)16 * LDS * sizeof(bf16) + (ATTN_ALIAS ? (sm_kv > sm_red ? sm_kv : sm_red) : sm_kv + sm_red);
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_pre);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(sm_pre_plain + (EXT ? BIAS_SMEM_MAX : 0)));
         if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_dec);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
