@@ -85,3 +85,24 @@ def test_a_random_folder_is_read_by_the_plain_reader(tmp_path):
     del raw["layers"][0]["mixer"]["buckets"]
     json.dump(raw, open(os.path.join(d, "config.json"), "w"))
     assert u.config_from_dir(d).layers[0].mixer.buckets == 6
+
+
+def test_the_bench_models_are_configurations_of_equal_active_size():
+    """The models that ``bench.py --only vusalix`` times: a Vusalix whose chosen and shared experts together have the dense
+    models' inner size, and whose latent layers' key row is one the tensor-core attention takes."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    import ultima_b200 as u
+    for z in bench.SUGIZEN_SIZES.values():
+        cfg = u.config_from_dict(bench.vusalix_config(z))
+        spec = u.model_spec_for(cfg)
+        assert spec.streams == 2 and len(cfg.layers) == z["layers"]
+        kinds = [L.kind for L in cfg.layers]
+        assert set(kinds) == {"attention", "delta", "latent_attention"}
+        for L in cfg.layers:
+            f = L.mlp
+            assert f.top * f.ff + f.shared_ff == z["ff"]
+            if L.kind == "latent_attention":
+                assert L.mixer.kv_rank + L.mixer.rot_dim == 256

@@ -313,7 +313,7 @@ def _engine(folder, dtype, **kw):
 
 
 def _for(name, dtype):
-    """The model's folder for a run in ``dtype``.  In bfloat16 a router's close call between two outputs may go either
+    """The model's folder for a run in ``dtype``.  In bfloat16 a router's near tie between two outputs may go either
     way, and one other choice reaches every later position through states and keys; so the bfloat16 runs of whole
     models use the same models with routers that choose every output (the weights still differ from token to token).
     The choice itself is held to the plain implementation by the 32-bit runs of the same models, by the one-layer

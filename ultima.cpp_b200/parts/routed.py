@@ -31,7 +31,7 @@ class RoutedExperts(FeedForward):
     scores are s + correction (a stored vector); with ``groups`` = (count, keep) the outputs form ``count`` equal
     groups of neighbours, a group's score is its largest choice score, and only outputs of the ``keep`` best groups can
     be chosen (the others count as -inf); the ``top`` largest choice scores are chosen and weighted with their s, not
-    renormalised.  The last ``n_identity`` outputs are identity experts: they hand the input on (times the weight) and
+    renormalised.  The last ``n_identity`` outputs are identity experts: they hand the input on, scaled by the choice's weight, and
     have no tensors.  ``shared_inner``: one more gated feed-forward that every token uses, added unweighted.
 
     On the GPU: the router's product with float32 sums (CUDA cores and float32 weights; in a bfloat16 run the stored
