@@ -541,7 +541,8 @@ def design_times(args, only, models):
             spec = u.model_spec_for(cfg)
             tensors = random_tensors_on_device(spec.weight_specs(), 0, torch.bfloat16, dev)
             engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=B * (args.prompt + 256) + P + 64, max_seqs=B + 1,
-                            max_step_tokens=max(P, 2048), max_context=max(args.prompt + 256, P + 64), with_sampler=False)
+                            max_step_tokens=max(P, 2048), max_context=max(args.prompt + 256, P + 64), with_sampler=False,
+                            window_pass=args.window_pass)
             del tensors
             engine.warm_up()
             V = engine.spec.vocab_size
@@ -966,6 +967,9 @@ def main():
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the timed prompt")
+    ap.add_argument("--window-pass", type=int, default=2048,
+                    help="--only sugizen/tinuzen/vusalix: tokens a sequence brings in one pass where layers have windows "
+                         "(the engine's own default is 1024)")
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds after which a run that has not ended dumps its stack and exits (0: never)")
     args = ap.parse_args()

@@ -517,6 +517,11 @@ def test_prompt_against_token_by_token_and_portions(folders, name):
     # the same through passes inside one step (a step cut at 16 tokens)
     small = _engine(d, "float32", max_step_tokens=16)
     agree(_whole(small, ids), ref, "float32", 4, (name, "passes"))
+    # and with a windowed layer's ring sized for passes shorter and longer than the windows
+    for wp in (24, 2048):
+        eng2 = _engine(d, "float32", window_pass=wp, poison_cache=True)
+        agree(_whole(eng2, ids), ref, "float32", 4, (name, "window_pass", wp))
+        agree(_prompt_then_single_tokens(eng2, ids, 97), ref, "float32", 4, (name, "window_pass then tokens", wp))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

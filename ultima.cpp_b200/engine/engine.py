@@ -46,12 +46,15 @@ class Engine:
                      to a page of 64; sizes the cache
     max_seqs         slots (sequences alive at once)
     max_step_tokens  tokens of one pass through the layers; longer steps are cut into passes
+    window_pass      where layers have windows: the most tokens ONE sequence brings in a pass.  A windowed layer's
+                     ring holds window + this many positions a slot, so it trades cache for longer passes (fewer
+                     launches a prompt, and a routed feed-forward's experts share their matrices over more rows)
     """
 
     def __init__(self, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096,
                  max_seqs: int | None = None, max_step_tokens: int = 4096, device="cuda:0",
                  max_context: int | None = None, poison_cache: bool = False, runtime=None,
-                 use_graphs: bool = True, with_sampler: bool = True):
+                 use_graphs: bool = True, with_sampler: bool = True, window_pass: int = 1024):
         self.spec = spec
         self.dtype = _dtype_of(dtype)
         self.device = torch.device(device)
@@ -73,7 +76,9 @@ class Engine:
                    if isinstance(n, KVNeed) and n.window is not None]
         # a sequence brings at most this many tokens in one pass; with windows it also
         # bounds the span a windowed group must hold
-        self.seq_chunk = self.max_step_tokens if not windows else min(self.max_step_tokens, 1024)
+        if int(window_pass) < 1:
+            raise ValueError("window_pass must be at least 1")
+        self.seq_chunk = self.max_step_tokens if not windows else min(self.max_step_tokens, int(window_pass))
         self.cache = Cache(needs, self.model.cache_sources(), self.max_tokens, self.max_context,
                            n_slots, self.seq_chunk, dtype=self.rt.cache_dtype, device=self.device,
                            poison=poison_cache)
