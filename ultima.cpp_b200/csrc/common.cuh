@@ -1,6 +1,7 @@
 // Shared helpers of the kernels: element types, conversions, reductions, launch checks.
 #pragma once
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <stdint.h>
 
@@ -32,6 +33,25 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // Launch ``kern`` as a programmatic dependent of the kernel before it in the stream: it may begin
 // while that kernel still runs, so it must call pdl_wait() before it reads or writes anything the
 // earlier kernels touch, and before any thread returns.
+// ``dependent`` false: an ordinary launch, which starts when the kernels before it have ended (pdl_wait and pdl_trigger
+// then do nothing).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ub_launch_ordered(bool dependent, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const int plain = [] { const char* v = getenv("ULTIMA_PDL"); return v && v[0] == '0'; }();   // for measurements
+    cfg.numAttrs = (plain || !dependent) ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t ub_launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                               cudaStream_t st, Args... args) {
@@ -44,7 +64,8 @@ static inline cudaError_t ub_launch_dependent(void (*kern)(KArgs...), dim3 grid,
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    static const int plain = [] { const char* v = getenv("ULTIMA_PDL"); return v && v[0] == '0'; }();   // for measurements
+    cfg.numAttrs = plain ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 

@@ -365,8 +365,8 @@ UB_API int ub_ssm_conv_state_update(const float* p, long long ldp, int n_parts, 
 }
 
 UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, const float* Dw, float* y, float* S,
-                       const int* seq_start, const int* seq_slot, int n_seqs, int H, int P, int N, int G, int sm_count,
-                       cudaStream_t st) {
+                       const int* seq_start, const int* seq_slot, int n_seqs, int n_tokens, int H, int P, int N, int G,
+                       int sm_count, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || P <= 0 || N <= 0 || N > 256 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
     const int lanes = N >= 128 ? 32 : (N >= 64 ? 16 : 8);
@@ -379,6 +379,9 @@ UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, con
     const int per = (N + lanes - 1) / lanes;               // at most 8: N <= 256
     const bool vec = N % 4 == 0 && P % 4 == 0 && (((uintptr_t)xbc) & 15) == 0;
     cudaError_t e;
+    // a step of more than one token a sequence: an ordinary launch, so that the blocks, each busy for the whole step, are
+    // spread over idle SMs instead of being placed where the kernel before happens to drain first (as the delta rule's scan)
+    const bool dep = n_tokens <= n_seqs;
 #define GO4(RR, LL, CC, VV) do { \
         constexpr size_t smem = SsmScanLayout<RR, LL, CC>::BYTES; \
         static bool attr_done = false; \
@@ -387,7 +390,7 @@ UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, con
             if (e != cudaSuccess) return (int)e; \
             attr_done = true; \
         } \
-        e = ub_launch_dependent(ssm_scan_kernel<RR, LL, CC, VV>, grid, block, smem, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G); \
+        e = ub_launch_ordered(dep, ssm_scan_kernel<RR, LL, CC, VV>, grid, block, smem, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G); \
     } while (0)
 #define GO3(RR, LL, CC) do { if (vec) GO4(RR, LL, CC, true); else GO4(RR, LL, CC, false); } while (0)
 #define GO2(RR, LL) do { if (cpt == 2) GO3(RR, LL, 2); else GO3(RR, LL, 1); } while (0)

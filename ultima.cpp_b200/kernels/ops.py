@@ -132,11 +132,11 @@ def _declare(lib, source: str) -> None:
                                             I, I, I, F, I, P, P]},
         "delta.cu": {"ub_delta_prepare": [P, L, I, L, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
                      "ub_conv_state_update": [P, L, I, L, P, P, P, I, I, I, P],
-                     "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+                     "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
                      "ub_delta_finish": [P, P, L, I, L, I, P, P, I, I, I, I, F, P]},
         "ssm.cu": {"ub_ssm_prepare": [P, L, I, L, P, P, P, P, I, P, P, P, P, P, P, P, P, I, P],
                    "ub_ssm_conv_state_update": [P, L, I, L, P, P, P, P, I, P],
-                   "ub_ssm_scan": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+                   "ub_ssm_scan": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
                    "ub_ssm_finish": [P, P, L, I, L, P, P, P, I, I, I, F, F, P]},
         "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P, P, I, P], "ub_sample_params_size": []},
     }.get(source, {})
@@ -661,7 +661,7 @@ def ssm_scan(xbc, dtv, dec, d_skip, y, state, batch, H, P, N, G):
     for t in (xbc, dtv, dec, d_skip, y):
         assert t.dtype == torch.float32 and t.is_contiguous()
     _check(_lib("ssm.cu").ub_ssm_scan(_ptr(xbc), _ptr(dtv), _ptr(dec), _ptr(d_skip), _ptr(y), _ptr(state), _ptr(batch.seq_start),
-                                      _ptr(batch.seq_slot), batch.n_seqs, H, P, N, G, sm_count(), _stream()), "ssm_scan")
+                                      _ptr(batch.seq_slot), batch.n_seqs, xbc.shape[0], H, P, N, G, sm_count(), _stream()), "ssm_scan")
 
 
 def ssm_finish(y, p, shape, weight, out, n_groups, eps, scale=1.0):
@@ -726,7 +726,7 @@ def delta_scan(qn, kn, vc, beta, dec, out, state, batch, H, G, D, E):
     _need_cuda(qn, kn, vc, beta, dec, out, state)
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, D, E)
     _check(_lib("delta.cu").ub_delta_scan(_ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(dec), _ptr(out), _ptr(state),
-                                          _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, H, G, D, E, sm_count(),
+                                          _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, qn.shape[0], H, G, D, E, sm_count(),
                                           _stream()),
            "delta_scan")
 
