@@ -125,6 +125,37 @@ def test_the_router_chooses_by_corrected_scores_within_the_kept_groups_and_weigh
         assert set(got) == set(want), (t, got, want)
         assert all(abs(got[e] - want[e]) < 1e-6 for e in want), (t, got, want)
     assert counts.cpu().tolist() == torch.bincount(ref_idx[ref_idx < ne].flatten(), minlength=ne).tolist()
+    # a step of few tokens: routing, plan and places in one launch agree with the three kernels
+    Ts, tile = min(T, ops.ROUTE_SMALL_TOKENS), 16
+    zs = z[:Ts].contiguous().to(DEV)
+    i3, w3 = torch.empty(Ts, top, dtype=torch.int32, device=DEV), torch.empty(Ts, top, device=DEV)
+    ws = torch.zeros(3 * ne + 4, dtype=torch.int32, device=DEV)
+    max_tiles = Ts * top + ne
+    t3, rp3, sr3 = (torch.full((max_tiles, 4), -7, dtype=torch.int32, device=DEV), torch.empty(Ts, top, dtype=torch.int32, device=DEV),
+                    torch.full((Ts * top,), -7, dtype=torch.int32, device=DEV))
+    ops.route(zs, corr.to(DEV), ne, top, groups[0] if groups else 1, groups[1] if groups else 1, i3, w3, ws[:ne])
+    ops.route_plan(ws[:ne], ws[ne:2 * ne], ws[2 * ne:3 * ne], t3, ws[3 * ne:3 * ne + 1], ne, tile)
+    ops.route_scatter(i3, ws[2 * ne:3 * ne], ws[ne:2 * ne], rp3, sr3, ne)
+    i1, w1 = torch.empty_like(i3), torch.empty_like(w3)
+    t1, rp1, sr1, n1 = torch.full_like(t3, -7), torch.empty_like(rp3), torch.full_like(sr3, -7), torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.route_small(zs, corr.to(DEV), ne, top, groups[0] if groups else 1, groups[1] if groups else 1, i1, w1, t1, n1, rp1, sr1, tile)
+    n = int(n1.item())
+    assert torch.equal(i1, i3) and torch.equal(w1, w3) and n == int(ws[3 * ne].item()) and torch.equal(t1[:n, :3], t3[:n, :3])
+    # places within an expert's segment are handed out in any order: the same tokens, and every choice at a row of its expert
+    seg = {}
+    for e, r0, k in t1[:n, :3].cpu().tolist():
+        lo, hi = seg.get(e, (r0, r0))
+        seg[e] = (min(lo, r0), max(hi, r0 + k))
+    rp, sr, ii = rp1.cpu(), sr1.cpu(), i1.cpu()
+    for t in range(Ts):
+        for k in range(top):
+            e, p = int(ii[t, k]), int(rp[t, k])
+            if e >= ne:
+                assert p == -1
+            else:
+                assert seg[e][0] <= p < seg[e][1] and int(sr[p]) == t
+    live = rp[rp >= 0]
+    assert live.numel() == len(set(live.tolist())) == int((ii < ne).sum())
     # the same logits handed over as three K slices whose sum they are
     coarse = (z * 4).round() / 4
     rest = z - coarse

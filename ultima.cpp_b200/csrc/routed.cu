@@ -22,20 +22,13 @@
 
 constexpr int ROUTE_WARPS = 4;
 
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
-route_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long part_stride, const float* __restrict__ corr,
-             int n_tokens, int n_out, int n_experts, int top, int n_groups, int keep, int* __restrict__ idx,
-             float* __restrict__ wts, int* __restrict__ counts) {
-    extern __shared__ float sm[];
-    pdl_trigger();
-    pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long t = (long long)blockIdx.x * ROUTE_WARPS + warp;
-    if (t >= n_tokens) return;
-    float* sc = sm + (size_t)warp * (2 * n_out + n_groups);      // scores
-    float* ch = sc + n_out;                                      // choice scores
-    float* gm = ch + n_out;                                      // a group's best choice score
-    const float* zr = z + t * ldz;
+// One token's routing by one warp: zr its logits (``n_parts`` slices ``part_stride`` apart), sc / ch / gm the warp's
+// work space ([n_out], [n_out], [n_groups]), idx_t / wts_t the token's ``top`` results, counts the experts' row counters
+// (global or shared memory).
+__device__ __forceinline__ void route_token(const float* __restrict__ zr, int n_parts, long long part_stride,
+                                            const float* __restrict__ corr, int n_out, int n_experts, int top, int n_groups,
+                                            int keep, float* sc, float* ch, float* gm, int lane, int* idx_t, float* wts_t,
+                                            int* counts) {
     float m = -INFINITY;
     for (int i = lane; i < n_out; i += 32) {              // the logits may come as K slices: summed in the slices' order
         float v = zr[i];
@@ -91,12 +84,81 @@ route_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long 
         }
         if (at == 0x7fffffff) at = 0;                     // (every score was taken or not a number: a row of NaN)
         if (lane == 0) {
-            idx[t * top + k] = at;
-            wts[t * top + k] = sc[at];
+            idx_t[k] = at;
+            wts_t[k] = sc[at];
             ch[at] = NAN;                                 // taken: NaN is passed over, while -inf may still be chosen
             if (at < n_experts) atomicAdd(&counts[at], 1);
         }
         __syncwarp();
+    }
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long part_stride, const float* __restrict__ corr,
+             int n_tokens, int n_out, int n_experts, int top, int n_groups, int keep, int* __restrict__ idx,
+             float* __restrict__ wts, int* __restrict__ counts) {
+    extern __shared__ float sm[];
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = (long long)blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= n_tokens) return;
+    float* sc = sm + (size_t)warp * (2 * n_out + n_groups);      // scores
+    float* ch = sc + n_out;                                      // choice scores
+    float* gm = ch + n_out;                                      // a group's best choice score
+    route_token(z + t * ldz, n_parts, part_stride, corr, n_out, n_experts, top, n_groups, keep, sc, ch, gm, lane,
+                idx + t * top, wts + t * top, counts);
+}
+
+// route, plan and scatter of a step of few tokens in ONE block (the counters live in shared memory; the global ones are
+// not touched and stay zero): three launches of a decode step become one.
+constexpr int SMALL_WARPS = 8;
+
+__global__ void __launch_bounds__(SMALL_WARPS * 32)
+route_small_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long part_stride, const float* __restrict__ corr,
+                   int n_tokens, int n_out, int n_experts, int top, int n_groups, int keep, int* __restrict__ idx,
+                   float* __restrict__ wts, int4* __restrict__ tiles, int* __restrict__ n_tiles, int* __restrict__ row_pos,
+                   int* __restrict__ src_rows, int tile) {
+    extern __shared__ float sm[];
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_warp = 2 * n_out + n_groups;
+    int* cnt = (int*)(sm + (size_t)SMALL_WARPS * per_warp);     // [n_experts] rows of every expert
+    int* cursor = cnt + n_experts;                              // [n_experts] places handed out
+    int* seg = cursor + n_experts;                              // [n_experts] first sorted row
+    int* first_tile = seg + n_experts;                          // [n_experts + 1]
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) { cnt[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    float* sc = sm + (size_t)warp * per_warp;
+    for (int t = warp; t < n_tokens; t += SMALL_WARPS) {
+        route_token(z + (long long)t * ldz, n_parts, part_stride, corr, n_out, n_experts, top, n_groups, keep, sc, sc + n_out,
+                    sc + 2 * n_out, lane, idx + (long long)t * top, wts + (long long)t * top, cnt);
+        __syncwarp();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int row = 0, tl = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            seg[e] = row;
+            first_tile[e] = tl;
+            row += cnt[e];
+            tl += (cnt[e] + tile - 1) / tile;
+        }
+        first_tile[n_experts] = tl;
+        *n_tiles = tl;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int n = cnt[e], r0 = seg[e];
+        for (int i = 0; i * tile < n; ++i) tiles[first_tile[e] + i] = make_int4(e, r0 + i * tile, min(tile, n - i * tile), 0);
+    }
+    for (int i = threadIdx.x; i < n_tokens * top; i += blockDim.x) {
+        const int e = idx[i];                                   // written by this block before the barriers above
+        if (e >= n_experts) { row_pos[i] = -1; continue; }
+        const int p = seg[e] + atomicAdd(&cursor[e], 1);
+        row_pos[i] = p;
+        src_rows[p] = i / top;
     }
 }
 
@@ -215,6 +277,24 @@ UB_API int ub_route(const float* z, long long ldz, int n_parts, long long part_s
     const unsigned grid = (unsigned)((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS);
     return (int)ub_launch_dependent(route_kernel, dim3(grid), dim3(ROUTE_WARPS * 32), smem, st, z, ldz, n_parts, part_stride, corr,
                                     n_tokens, n_out, n_experts, top, n_groups, keep, idx, wts, counts);
+}
+
+// The three steps above in one launch, for steps of at most ROUTE_SMALL_TOKENS tokens.
+constexpr int ROUTE_SMALL_TOKENS = 64;
+UB_API int ub_route_small_tokens() { return ROUTE_SMALL_TOKENS; }
+
+UB_API int ub_route_small(const float* z, long long ldz, int n_parts, long long part_stride, const float* corr, int n_tokens,
+                          int n_out, int n_experts, int top, int n_groups, int keep, int* idx, float* wts, void* tiles,
+                          int* n_tiles, int* row_pos, int* src_rows, int tile, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (n_parts < 1 || n_tokens > ROUTE_SMALL_TOKENS || tile < 1) return UB_ERR_ARG;
+    if (n_out < 1 || n_experts < 1 || n_experts > n_out || top < 1 || top > n_out || n_groups < 1 || n_out % n_groups ||
+        keep < 1 || keep > n_groups) return UB_ERR_ARG;
+    const size_t smem = (size_t)SMALL_WARPS * (2 * n_out + n_groups) * sizeof(float) + (size_t)(4 * n_experts + 1) * sizeof(int);
+    if (smem > 48 * 1024) return UB_ERR_ARG;
+    return (int)ub_launch_dependent(route_small_kernel, dim3(1), dim3(SMALL_WARPS * 32), smem, st, z, ldz, n_parts, part_stride,
+                                    corr, n_tokens, n_out, n_experts, top, n_groups, keep, idx, wts, (int4*)tiles, n_tiles,
+                                    row_pos, src_rows, tile);
 }
 
 UB_API int ub_route_plan(int* counts, int* cursor, int* seg_start, void* tiles, int* n_tiles, int n_experts, int tile,

@@ -122,6 +122,7 @@ def _declare(lib, source: str) -> None:
         "routed.cu": {"ub_route": [P, L, I, L, P, I, I, I, I, I, I, P, P, P, P],
                       "ub_route_plan": [P, P, P, P, P, I, I, P],
                       "ub_route_scatter": [P, P, P, P, P, I, I, I, P],
+                      "ub_route_small": [P, L, I, L, P, I, I, I, I, I, I, P, P, P, P, P, P, I, P],
                       "ub_route_combine": [P, I, P, I, P, P, P, I, I, I, P],
                       "ub_route_gather": [P, P, P, I, I, L, P]},
         "latent.cu": {"ub_latent_place": [P, I, L, I, L, I, I, P, P, I, P, P, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P]},
@@ -561,6 +562,26 @@ def route(z, correction, n_experts, top, n_groups, keep, idx, wts, counts):
     assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == n_out)
     _check(_lib("routed.cu").ub_route(_ptr(z), ldz, n_parts, part_stride, _ptr(correction), T, n_out, n_experts, top, n_groups, keep,
                                       _ptr(idx), _ptr(wts), _ptr(counts), _stream()), "route")
+
+
+ROUTE_SMALL_TOKENS = 64      # steps of at most this many tokens: route, plan and scatter as one launch (csrc/routed.cu)
+
+
+def route_small(z, correction, n_experts, top, n_groups, keep, idx, wts, tiles, n_tiles, row_pos, src_rows, tile):
+    """``route``, ``route_plan`` and ``route_scatter`` of a step of at most ROUTE_SMALL_TOKENS tokens in one launch of one
+    block; the counters of the separate kernels are not used."""
+    _need_cuda(z, correction, idx, wts, tiles, n_tiles, row_pos, src_rows)
+    T, ldz, n_parts, part_stride = _parts_of(z)
+    n_out = z.shape[-1]
+    assert T <= ROUTE_SMALL_TOKENS and z.dtype == torch.float32 and z.stride(-1) == 1
+    assert idx.dtype == torch.int32 and wts.dtype == torch.float32 and idx.is_contiguous() and wts.is_contiguous()
+    assert idx.shape == wts.shape == (T, top) and row_pos.dtype == src_rows.dtype == torch.int32
+    assert row_pos.is_contiguous() and row_pos.numel() == T * top and src_rows.numel() >= T * top
+    assert tiles.dtype == torch.int32 and tiles.is_contiguous() and n_tiles.dtype == torch.int32
+    assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == n_out)
+    _check(_lib("routed.cu").ub_route_small(_ptr(z), ldz, n_parts, part_stride, _ptr(correction), T, n_out, n_experts, top,
+                                            n_groups, keep, _ptr(idx), _ptr(wts), _ptr(tiles), _ptr(n_tiles), _ptr(row_pos),
+                                            _ptr(src_rows), tile, _stream()), "route_small")
 
 
 def route_plan(counts, cursor, seg_start, tiles, n_tiles, n_experts, tile=ROUTE_TILE):

@@ -96,6 +96,8 @@ class RoutedExperts(FeedForward):
             self.w_down[e] = tensors[f"experts.{e}.down_proj.weight"]
         if self.shared is not None:
             self.shared.bind({w.name: tensors["shared." + w.name] for w in self.shared.weight_specs()}, rt)
+        # the one-block routing kernel keeps eight warps' work space and the experts' counters in 48 KB of shared memory
+        self._small_fits = 8 * (2 * self.n_out + self.groups[0]) * 4 + (4 * self.ne + 1) * 4 <= 48 * 1024
         # counters of the routing kernels, shared by the model's routed layers (one runs at a time): rows of every
         # expert, hand-out cursors, first sorted row of every expert, number of tiles
         self.ws = rt.shared(("routed_counters", self.ne), lambda: torch.zeros(3 * self.ne + 4, dtype=torch.int32, device=rt.device))
@@ -124,10 +126,14 @@ class RoutedExperts(FeedForward):
         max_tiles = min(T * top, -(-T * top // tile) + ne)
         tiles = rt.arena.alloc((max_tiles, 4), i32)
         counts, cursor, seg_start, n_tiles = self.ws[:ne], self.ws[ne:2 * ne], self.ws[2 * ne:3 * ne], self.ws[3 * ne:3 * ne + 1]
-        rt.launches += 3
-        ops.route(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, counts)
-        ops.route_plan(counts, cursor, seg_start, tiles, n_tiles, ne, tile)
-        ops.route_scatter(idx, seg_start, cursor, row_pos, src_rows, ne)
+        if T <= ops.ROUTE_SMALL_TOKENS and self._small_fits:
+            rt.launches += 1                  # few tokens: the three steps as one launch of one block
+            ops.route_small(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, tiles, n_tiles, row_pos, src_rows, tile)
+        else:
+            rt.launches += 3
+            ops.route(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, counts)
+            ops.route_plan(counts, cursor, seg_start, tiles, n_tiles, ne, tile)
+            ops.route_scatter(idx, seg_start, cursor, row_pos, src_rows, ne)
         plan = RoutePlan(tiles, n_tiles, src_rows, max_tiles, T * top, tile=tile)
         if fast:
             rows = rt.arena.alloc((T * top, self.width), rt.dtype)
