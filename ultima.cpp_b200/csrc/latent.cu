@@ -40,26 +40,29 @@ latent_place_kernel(const TX* __restrict__ x, long long ldx, int n_parts, long l
         const float cj = cs[(long long)pos * half + j], sj = sn[(long long)pos * half + j];
         return (d & 1) ? self * cj + mate * sj : self * cj - mate * sj;
     };
-    float ss = 0.f;
-    for (int i = tid; i < rank + rot; i += blockDim.x) {
-        const float v = at(c_off + i);
-        row[i] = v;
-        if (i < rank) ss += v * v;
-    }
-    ss = block_sum(ss, red);                          // (also orders the writes of row before the reads below)
-    const float inv = inv_rms(ss, (float)rank, eps);
-    TC* dst = kc + paged_offset(c, seq, pos, 0);
-    for (int i = tid; i < rank + rot; i += blockDim.x) {
-        float o;
-        if (i < rank) o = row[i] * inv * cw[i];
-        else {
-            const int d = i - rank;
-            o = (cs && d < rd) ? turned(row[i], row[rank + (d ^ 1)], d) : row[i];
+    if (blockIdx.y == 0) {                            // the latent columns: the first block of the token's row of blocks
+        float ss = 0.f;
+        for (int i = tid; i < rank + rot; i += blockDim.x) {
+            const float v = at(c_off + i);
+            row[i] = v;
+            if (i < rank) ss += v * v;
         }
-        dst[i] = from_f32<TC>(o);
+        ss = block_sum(ss, red);                      // (also orders the writes of row before the reads below)
+        const float inv = inv_rms(ss, (float)rank, eps);
+        TC* dst = kc + paged_offset(c, seq, pos, 0);
+        for (int i = tid; i < rank + rot; i += blockDim.x) {
+            float o;
+            if (i < rank) o = row[i] * inv * cw[i];
+            else {
+                const int d = i - rank;
+                o = (cs && d < rd) ? turned(row[i], row[rank + (d ^ 1)], d) : row[i];
+            }
+            dst[i] = from_f32<TC>(o);
+        }
     }
+    // the query columns, shared out over the token's blocks (a step of few tokens launches several a token)
     const int qd = dim + rot;
-    for (int i = tid; i < nh * qd; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + tid; i < nh * qd; i += blockDim.x * gridDim.y) {
         const int h = i / qd, d = i % qd;
         const float v = at(q_off + i);
         if (d < dim) { q_plain[(t * nh + h) * dim + d] = from_f32<TQ>(v); continue; }
@@ -82,7 +85,10 @@ UB_API int ub_latent_place(const void* x, int x_dtype, long long ldx, int n_part
     if (smem > 48 * 1024) return UB_ERR_ARG;
     PagedKV c{table, pages_per_seq, ring, page, 1, rank + rot};
     cudaError_t e;
-#define GO(TX, TQ, TC) e = ub_launch_dependent(latent_place_kernel<TX, TQ, TC>, dim3(n_tokens), dim3(256), smem, st, (const TX*)x, ldx, \
+    // blocks a token: one for a prompt's many tokens; for few tokens as many as give every thread one query column, up to 16
+    const int cols = nh * (dim + rot);
+    const int per_token = n_tokens > 64 ? 1 : min(16, max(1, (cols + 255) / 256));
+#define GO(TX, TQ, TC) e = ub_launch_dependent(latent_place_kernel<TX, TQ, TC>, dim3(n_tokens, per_token), dim3(256), smem, st, (const TX*)x, ldx, \
         n_parts, part_stride, q_off, c_off, (TQ*)q_plain, (TQ*)q_lat, cw, cs, sn, rd, tok_pos, tok_seq, (TC*)kcache, c, nh, dim, \
         rot, rank, eps)
     if (x_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float, float);
