@@ -112,7 +112,7 @@ route_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long 
 
 // route, plan and scatter of a step of few tokens in ONE block (the counters live in shared memory; the global ones are
 // not touched and stay zero): three launches of a decode step become one.
-constexpr int SMALL_WARPS = 8;
+constexpr int SMALL_WARPS = 16;          // a token a warp: more tokens than warps and the separate kernels are faster
 
 __global__ void __launch_bounds__(SMALL_WARPS * 32)
 route_small_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long part_stride, const float* __restrict__ corr,
@@ -280,7 +280,7 @@ UB_API int ub_route(const float* z, long long ldz, int n_parts, long long part_s
 }
 
 // The three steps above in one launch, for steps of at most ROUTE_SMALL_TOKENS tokens.
-constexpr int ROUTE_SMALL_TOKENS = 64;
+constexpr int ROUTE_SMALL_TOKENS = SMALL_WARPS;
 UB_API int ub_route_small_tokens() { return ROUTE_SMALL_TOKENS; }
 
 UB_API int ub_route_small(const float* z, long long ldz, int n_parts, long long part_stride, const float* corr, int n_tokens,

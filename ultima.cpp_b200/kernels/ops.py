@@ -564,7 +564,7 @@ def route(z, correction, n_experts, top, n_groups, keep, idx, wts, counts):
                                       _ptr(idx), _ptr(wts), _ptr(counts), _stream()), "route")
 
 
-ROUTE_SMALL_TOKENS = 64      # steps of at most this many tokens: route, plan and scatter as one launch (csrc/routed.cu)
+ROUTE_SMALL_TOKENS = 16      # steps of at most this many tokens (a warp each): route, plan and scatter as one launch (csrc/routed.cu)
 
 
 def route_small(z, correction, n_experts, top, n_groups, keep, idx, wts, tiles, n_tiles, row_pos, src_rows, tile):

@@ -96,8 +96,8 @@ class RoutedExperts(FeedForward):
             self.w_down[e] = tensors[f"experts.{e}.down_proj.weight"]
         if self.shared is not None:
             self.shared.bind({w.name: tensors["shared." + w.name] for w in self.shared.weight_specs()}, rt)
-        # the one-block routing kernel keeps eight warps' work space and the experts' counters in 48 KB of shared memory
-        self._small_fits = 8 * (2 * self.n_out + self.groups[0]) * 4 + (4 * self.ne + 1) * 4 <= 48 * 1024
+        # the one-block routing kernel keeps sixteen warps' work space and the experts' counters in 48 KB of shared memory
+        self._small_fits = 16 * (2 * self.n_out + self.groups[0]) * 4 + (4 * self.ne + 1) * 4 <= 48 * 1024
         # counters of the routing kernels, shared by the model's routed layers (one runs at a time): rows of every
         # expert, hand-out cursors, first sorted row of every expert, number of tiles
         self.ws = rt.shared(("routed_counters", self.ne), lambda: torch.zeros(3 * self.ne + 4, dtype=torch.int32, device=rt.device))
