@@ -13,6 +13,7 @@ from . import qwen3  # registers Qwen3ForCausalLM
 from . import sugizen  # registers Sugizen
 from . import tinuzen  # registers Tinuzen
 from . import vusalix  # registers Vusalix
+from . import bizepel  # registers Bizepel
 
 for _name in filter(None, (m.strip() for m in os.environ.get("ULTIMA_ARCH_MODULES", "").split(","))):
     importlib.import_module(_name)

@@ -79,9 +79,13 @@ class KVGroup:
 
 
 class StateGroup:
-    def __init__(self, need: StateNeed, runs: list, n_slots: int, device):
-        self.need, self.runs = need, list(runs)
-        self.index = {r: i for i, r in enumerate(self.runs)}
+    """``entries``: (run, occurrence) pairs, one for each array of this shape a run asked for (a run may name the same
+    need more than once: two convolutions over channels of one width, say)."""
+
+    def __init__(self, need: StateNeed, entries: list, n_slots: int, device):
+        self.need, self.entries = need, list(entries)
+        self.runs = [r for r, _ in self.entries]
+        self.index = {e: i for i, e in enumerate(self.entries)}
         dt = getattr(torch, need.dtype)
         self.data = torch.zeros((len(self.runs), n_slots) + tuple(need.shape), dtype=dt, device=device)
 
@@ -104,7 +108,7 @@ class Cache:
         self.kv_groups: list[KVGroup] = []
         self.state_groups: list[StateGroup] = []
         self._kv_of_run: dict[int, KVGroup] = {}
-        self._state_of_run: dict[int, list] = {}             # run -> its StateGroups, in the order of its need
+        self._state_of_run: dict[int, list] = {}             # run -> (StateGroup, entry) pairs, in the order of its need
         self.cache_from = list(cache_from)
         total_pages = _ceil_div(self.max_tokens, PAGE)
         ctx_pages = _ceil_div(self.max_context, PAGE)
@@ -122,9 +126,8 @@ class Cache:
                 if isinstance(n, KVNeed):
                     kv_runs.setdefault(n, []).append(r)
                 elif isinstance(n, StateNeed):
-                    if n in st_order.setdefault(r, []):
-                        raise CacheError(f"run {r} names the same state twice: {n!r}")
-                    st_runs.setdefault(n, []).append(r)
+                    occurrence = st_order.setdefault(r, []).count(n)
+                    st_runs.setdefault(n, []).append((r, occurrence))
                     st_order[r].append(n)
                 elif n is not None:
                     raise CacheError(f"run {r}: unknown cache need {n!r}")
@@ -143,7 +146,7 @@ class Cache:
             g = by_need[need] = StateGroup(need, runs, self.n_slots, device)
             self.state_groups.append(g)
         for r, ns in st_order.items():
-            self._state_of_run[r] = [by_need[n] for n in ns]
+            self._state_of_run[r] = [(by_need[n], by_need[n].index[(r, ns[:i].count(n))]) for i, n in enumerate(ns)]
 
     # ---- slots ---------------------------------------------------------------------------
     def acquire(self) -> int:
@@ -233,7 +236,7 @@ class Cache:
                             g.need.window, owner)
         sgs = self._state_of_run.get(r)
         if sgs:
-            out.states = tuple(sg.data[sg.index[r]] for sg in sgs)
+            out.states = tuple(sg.data[i] for sg, i in sgs)
             out.state = out.states[0]
         return out
 

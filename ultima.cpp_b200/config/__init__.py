@@ -4,7 +4,8 @@ from .base import (ConfigError, ArchitectureConfig, ArchitectureEntry, register_
 from .qwen3 import Qwen3Config
 from .sugizen import SugizenConfig
 from .vusalix import VusalixConfig
+from .bizepel import BizepelConfig
 
 __all__ = ["ConfigError", "ArchitectureConfig", "ArchitectureEntry", "register_architecture", "find_architecture",
            "known_architectures", "read_config_json", "config_from_dict", "config_from_dir",
-           "Qwen3Config", "SugizenConfig", "VusalixConfig"]
+           "Qwen3Config", "SugizenConfig", "VusalixConfig", "BizepelConfig"]

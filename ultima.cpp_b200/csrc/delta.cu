@@ -158,18 +158,23 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 
 // VEC: sizes are multiples of 4 and every array starts on a 16-byte boundary, so tokens are fetched in
 // 16-byte copies, each thread keeping the same one or two places of a token's row for the whole launch.
-template <int R, int SCAN_LANES, bool VEC>
+//
+// GEN: the generalised rule, in which a token removes along its unit key u at a rate of its own for every key channel and
+// writes its raw key: with c = S_old^T u,  S[d, :] = w[d] S_old[d, :] - rem[d] c + kraw[d] v,  o = S^T q.  ``kn`` then holds
+// u, ``dec`` holds w, ``rem`` = rate * u and ``kraw`` come as two more arrays of the keys' shape, and ``beta`` is not read.
+template <int R, int SCAN_LANES, bool VEC, bool GEN>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vc,
                   const float* __restrict__ beta, const float* __restrict__ dec, float* __restrict__ out,
                   float* __restrict__ S, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
-                  int H, int G, int D, int E) {
+                  int H, int G, int D, int E, const float* __restrict__ rem, const float* __restrict__ kraw) {
     static_assert(R % 4 == 0, "a lane holds whole float4 chunks");
     constexpr int SCAN_COLS = 128 / SCAN_LANES;
     constexpr int DP = SCAN_LANES * R;
     constexpr int NC = R / 4;                             // chunks a lane
     constexpr int TT = DP <= 128 ? 8 : 4;                 // tokens a stage
     __shared__ __align__(16) float sq[2][TT][DP], sk[2][TT][DP], sa[2][TT][DP];
+    __shared__ __align__(16) float sr[GEN ? 2 : 1][GEN ? TT : 1][GEN ? DP : 4], sw[GEN ? 2 : 1][GEN ? TT : 1][GEN ? DP : 4];
     __shared__ __align__(16) float sv[2][TT][SCAN_COLS];
     __shared__ float sb[2][TT];
     __shared__ float so[TT][128];                          // the read-out's partial sums, [token][lane of the column][column]
@@ -192,18 +197,23 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     // columns past the sizes are constants that no copy ever touches
     for (int idx = tid; idx < 2 * TT * DP; idx += blockDim.x) {
         const int d = idx % DP;
-        if (d >= D) { (&sq[0][0][0])[idx] = 0.f; (&sk[0][0][0])[idx] = 0.f; (&sa[0][0][0])[idx] = 1.f; }
+        if (d >= D) {
+            (&sq[0][0][0])[idx] = 0.f; (&sk[0][0][0])[idx] = 0.f; (&sa[0][0][0])[idx] = 1.f;
+            if (GEN) { (&sr[0][0][0])[idx] = 0.f; (&sw[0][0][0])[idx] = 0.f; }
+        }
     }
     for (int idx = tid; idx < 2 * TT * SCAN_COLS; idx += blockDim.x)
         if (blockIdx.x * SCAN_COLS + idx % SCAN_COLS >= E) (&sv[0][0][0])[idx] = 0.f;
 
     // this thread's places in a token's [q | k | decay] row of 3 * D / 4 chunks (VEC)
-    int my_arr[2] = {-1, -1}, my_d[2] = {0, 0};
+    constexpr int NARR = GEN ? 5 : 3, NSL = GEN ? 3 : 2;          // arrays of the keys' shape; places a thread may hold
+    int my_arr[NSL], my_d[NSL];
+    for (int sl = 0; sl < NSL; ++sl) { my_arr[sl] = -1; my_d[sl] = 0; }
     if (VEC) {
         const int d4 = D >> 2;
-        for (int sl = 0; sl < 2; ++sl) {
+        for (int sl = 0; sl < NSL; ++sl) {
             const int c = tid + sl * (int)blockDim.x;
-            if (c < 3 * d4) { my_arr[sl] = c / d4; my_d[sl] = (c % d4) * 4; }
+            if (c < NARR * d4) { my_arr[sl] = c / d4; my_d[sl] = (c % d4) * 4; }
         }
     }
     const float* qrow = qn + (long long)g * D;
@@ -217,18 +227,20 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
             for (int tt = 0; tt < n; ++tt) {
                 const long long t = base + tt;
 #pragma unroll
-                for (int sl = 0; sl < 2; ++sl) {
+                for (int sl = 0; sl < NSL; ++sl) {
                     const int d = my_d[sl];
                     if (my_arr[sl] == 0) cp_async16(&sq[buf][tt][d], qrow + t * G * D + d);
                     else if (my_arr[sl] == 1) cp_async16(&sk[buf][tt][d], krow + t * G * D + d);
                     else if (my_arr[sl] == 2) cp_async16(&sa[buf][tt][d], arow + t * H * D + d);
+                    else if (GEN && my_arr[sl] == 3) cp_async16(&sr[GEN ? buf : 0][GEN ? tt : 0][d], rem + (t * G + g) * D + d);
+                    else if (GEN && my_arr[sl] == 4) cp_async16(&sw[GEN ? buf : 0][GEN ? tt : 0][d], kraw + (t * G + g) * D + d);
                 }
             }
             if (tid < n * (SCAN_COLS / 4)) {
                 const int tt = tid / (SCAN_COLS / 4), c = (tid % (SCAN_COLS / 4)) * 4;
                 if (blockIdx.x * SCAN_COLS + c < E) cp_async16(&sv[buf][tt][c], vrow + (long long)(base + tt) * H * E + c);
             }
-            if (tid >= 64 && tid < 64 + n) cp_async4(&sb[buf][tid - 64], beta + (long long)(base + tid - 64) * H + h);
+            if (!GEN && tid >= 64 && tid < 64 + n) cp_async4(&sb[buf][tid - 64], beta + (long long)(base + tid - 64) * H + h);
             asm volatile("cp.async.commit_group;" ::: "memory");
             return;
         }
@@ -238,13 +250,17 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
             cp_async4(&sq[buf][tt][d], qn + (t * G + g) * D + d);
             cp_async4(&sk[buf][tt][d], kn + (t * G + g) * D + d);
             cp_async4(&sa[buf][tt][d], dec + (t * H + h) * D + d);
+            if (GEN) {
+                cp_async4(&sr[GEN ? buf : 0][GEN ? tt : 0][d], rem + (t * G + g) * D + d);
+                cp_async4(&sw[GEN ? buf : 0][GEN ? tt : 0][d], kraw + (t * G + g) * D + d);
+            }
         }
         for (int idx = tid; idx < n * SCAN_COLS; idx += blockDim.x) {
             const int tt = idx / SCAN_COLS, c = idx % SCAN_COLS;
             const int jj = blockIdx.x * SCAN_COLS + c;
             if (jj < E) cp_async4(&sv[buf][tt][c], vc + ((long long)(base + tt) * H + h) * E + jj);
         }
-        if (tid < n) cp_async4(&sb[buf][tid], beta + (long long)(base + tid) * H + h);
+        if (!GEN && tid < n) cp_async4(&sb[buf][tid], beta + (long long)(base + tid) * H + h);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
@@ -263,6 +279,39 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
             const float4* a4 = reinterpret_cast<const float4*>(sa[buf][tt]);
             const float4* k4 = reinterpret_cast<const float4*>(sk[buf][tt]);
             const float4* q4 = reinterpret_cast<const float4*>(sq[buf][tt]);
+            if constexpr (GEN) {
+                const float4* r4 = reinterpret_cast<const float4*>(sr[buf][tt]);
+                const float4* w4 = reinterpret_cast<const float4*>(sw[buf][tt]);
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {                     // c = S_old^T u
+                    const float4 u4 = k4[c * SCAN_LANES + p];
+                    part[0] = fmaf(s[4 * c + 0], u4.x, part[0]);
+                    part[1] = fmaf(s[4 * c + 1], u4.y, part[1]);
+                    part[2] = fmaf(s[4 * c + 2], u4.z, part[2]);
+                    part[3] = fmaf(s[4 * c + 3], u4.w, part[3]);
+                }
+                float dot = (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+                for (int w = 1; w < SCAN_LANES; w <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
+                const float v = sv[buf][tt][col];
+                float op[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    const float4 a = a4[c * SCAN_LANES + p], rm = r4[c * SCAN_LANES + p], kw = w4[c * SCAN_LANES + p];
+                    const float4 q = q4[c * SCAN_LANES + p];
+                    s[4 * c + 0] = fmaf(kw.x, v, fmaf(-rm.x, dot, a.x * s[4 * c + 0]));
+                    s[4 * c + 1] = fmaf(kw.y, v, fmaf(-rm.y, dot, a.y * s[4 * c + 1]));
+                    s[4 * c + 2] = fmaf(kw.z, v, fmaf(-rm.z, dot, a.z * s[4 * c + 2]));
+                    s[4 * c + 3] = fmaf(kw.w, v, fmaf(-rm.w, dot, a.w * s[4 * c + 3]));
+                    op[0] = fmaf(s[4 * c + 0], q.x, op[0]);
+                    op[1] = fmaf(s[4 * c + 1], q.y, op[1]);
+                    op[2] = fmaf(s[4 * c + 2], q.z, op[2]);
+                    op[3] = fmaf(s[4 * c + 3], q.w, op[3]);
+                }
+                so[tt][p * SCAN_COLS + col] = (op[0] + op[1]) + (op[2] + op[3]);
+                return;
+            }
             float4 kk[NC];
             float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -323,7 +372,8 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
 template <typename TO>
 __global__ void __launch_bounds__(128)
 delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ z, long long ldz, int n_parts, long long part_stride,
-                    int silu_gate, const float* __restrict__ w, TO* __restrict__ out, int n_tokens, int H, int E, float eps) {
+                    int silu_gate, const float* __restrict__ w, TO* __restrict__ out, int n_tokens, int H, int E, float eps,
+                    int w_heads) {
     pdl_trigger();
     pdl_wait();
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -337,12 +387,73 @@ delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ z, lo
     ss = warp_sum(ss);
     const float inv = inv_rms(ss, (float)E, eps);
     const float* zrow = z + t * ldz + (long long)h * E;
+    if (w_heads) w += (long long)h * E;                   // a weight for every head instead of one shared by the heads
     for (int e = lane; e < E; e += 32) {
         float zv = 0.f;
         for (int i = 0; i < n_parts; ++i) zv += zrow[i * part_stride + e];
         const float g = silu_gate ? zv * sigmoidf_(zv) : sigmoidf_(zv);
         out[(t * H + h) * E + e] = from_f32<TO>(orow[e] * inv * w[e] * g);
     }
+}
+
+// The generalised delta rule's inputs, one warp a (token, head).  A projection row holds r, k, v (H heads of D) and the
+// removal rate's sums at their columns; ``wpre`` [T, H * D] holds the decay's sums (the low-rank product's result).
+//   u = k / sqrt(sum k^2 + unit_eps);  rem = sigmoid(a + a_bias) * u;  w = exp(-decay_scale * sigmoid(wpre + w0))
+// r, u, raw k, rem, w and v go out as [T, H * D] float32 each, the scan's operands.
+__global__ void __launch_bounds__(128)
+gdelta_prepare_kernel(const float* __restrict__ p, long long ldp, int n_parts, long long part_stride, int r_off, int k_off,
+                      int v_off, int a_off, const float* __restrict__ a_bias, const float* __restrict__ wpre,
+                      const float* __restrict__ w0, float* __restrict__ rn, float* __restrict__ un, float* __restrict__ kraw,
+                      float* __restrict__ rem, float* __restrict__ dec, float* __restrict__ vc, int n_tokens, int H, int D,
+                      float unit_eps, float decay_scale) {
+    pdl_trigger();
+    pdl_wait();
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)n_tokens * H) return;
+    const long long t = wid / H;
+    const int h = (int)(wid % H);
+    auto at = [&](int c) -> float {
+        float v = 0.f;
+        for (int i = 0; i < n_parts; ++i) v += p[i * part_stride + t * ldp + c];
+        return v;
+    };
+    float kv[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = lane + 32 * i;
+        kv[i] = d < D ? at(k_off + h * D + d) : 0.f;
+        ss += kv[i] * kv[i];
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + unit_eps);
+    const long long base = (t * H + h) * D;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= D) continue;
+        const int c = h * D + d;
+        const float u = kv[i] * inv;
+        un[base + d] = u;
+        kraw[base + d] = kv[i];
+        rem[base + d] = sigmoidf_(at(a_off + c) + a_bias[c]) * u;
+        dec[base + d] = expf(-decay_scale * sigmoidf_(wpre[base + d] + w0[c]));
+        rn[base + d] = at(r_off + c);
+        vc[base + d] = at(v_off + c);
+    }
+}
+
+UB_API int ub_gdelta_prepare(const float* p, long long ldp, int n_parts, long long part_stride, int r_off, int k_off, int v_off,
+                             int a_off, const float* a_bias, const float* wpre, const float* w0, float* rn, float* un,
+                             float* kraw, float* rem, float* dec, float* vc, int n_tokens, int H, int D, float unit_eps,
+                             float decay_scale, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (H <= 0 || D <= 0 || D > 256 || n_parts < 1) return UB_ERR_ARG;
+    const long long warps = (long long)n_tokens * H;
+    return (int)ub_launch_dependent(gdelta_prepare_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, st, p, ldp, n_parts,
+                                    part_stride, r_off, k_off, v_off, a_off, a_bias, wpre, w0, rn, un, kraw, rem, dec, vc,
+                                    n_tokens, H, D, unit_eps, decay_scale);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -385,10 +496,13 @@ UB_API int ub_conv_state_update(const float* p, long long ldp, int n_parts, long
 
 UB_API int ub_delta_scan(const float* qn, const float* kn, const float* vc, const float* beta, const float* dec, float* out,
                          float* S, const int* seq_start, const int* seq_slot, int n_seqs, int n_tokens, int H, int G, int D,
-                         int E, int sm_count, cudaStream_t st) {
+                         int E, int sm_count, const float* rem, const float* kraw, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
+    const bool gen = rem != nullptr;
+    if (gen != (kraw != nullptr)) return UB_ERR_ARG;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || D > 256 || E <= 0 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
-    const bool vec = D % 4 == 0 && E % 4 == 0 && (((uintptr_t)qn | (uintptr_t)kn | (uintptr_t)vc | (uintptr_t)dec) & 15) == 0;
+    const bool vec = D % 4 == 0 && E % 4 == 0 &&
+        (((uintptr_t)qn | (uintptr_t)kn | (uintptr_t)vc | (uintptr_t)dec | (uintptr_t)rem | (uintptr_t)kraw) & 15) == 0;
     // lanes a column: eight, and more (fewer values and a shorter chain a thread) only while the launch still has
     // no more than about one warp for every scheduler and every lane gets a whole float4 chunk; measured at 2,048
     // tokens, 16 heads, sizes of 128: 346 / 372 / 405 ns a token with 8 / 16 / 32 lanes, at sizes of 64: 322 / 296
@@ -409,26 +523,28 @@ UB_API int ub_delta_scan(const float* qn, const float* kn, const float* vc, cons
     // the kernel before drains, on the SMs that happen to have room first, several to an SM: measured, a prompt of 2,048
     // tokens with four such layers took 8.2 ms so and 6.6 ms with every CTA on an SM of its own.
     const bool dep = n_tokens <= n_seqs;
-#define GO(RR, LL) e = vec ? ub_launch_ordered(dep, delta_scan_kernel<RR, LL, true>, grid, block, 0, st, qn, kn, vc, beta, dec, out, S, seq_start, seq_slot, H, G, D, E) \
-                           : ub_launch_ordered(dep, delta_scan_kernel<RR, LL, false>, grid, block, 0, st, qn, kn, vc, beta, dec, out, S, seq_start, seq_slot, H, G, D, E)
+#define GO2(RR, LL, VV, GG) ub_launch_ordered(dep, delta_scan_kernel<RR, LL, VV, GG>, grid, block, 0, st, qn, kn, vc, beta, dec, out, S, seq_start, seq_slot, H, G, D, E, rem, kraw)
+#define GO(RR, LL) e = gen ? (vec ? GO2(RR, LL, true, true) : GO2(RR, LL, false, true)) : (vec ? GO2(RR, LL, true, false) : GO2(RR, LL, false, false))
     if (lanes == 32) { if (R == 4) GO(4, 32); else if (R == 8) GO(8, 32); else return UB_ERR_ARG; }
     else if (lanes == 16) { if (R == 4) GO(4, 16); else if (R == 8) GO(8, 16); else if (R == 16) GO(16, 16); else return UB_ERR_ARG; }
     else { if (R == 4) GO(4, 8); else if (R == 8) GO(8, 8); else if (R == 16) GO(16, 8); else GO(32, 8); }
 #undef GO
+#undef GO2
     return (int)e;
 }
 
 UB_API int ub_delta_finish(const float* o, const float* z, long long ldz, int n_parts, long long part_stride, int silu_gate,
-                           const float* w, void* out, int out_dtype, int n_tokens, int H, int E, float eps, cudaStream_t st) {
+                           const float* w, void* out, int out_dtype, int n_tokens, int H, int E, float eps, int w_heads,
+                           cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (n_parts < 1) return UB_ERR_ARG;
     const long long warps = (long long)n_tokens * H;
     const unsigned grid = (unsigned)((warps + 3) / 4);
     cudaError_t e;
     if (out_dtype == UB_F32)
-        e = ub_launch_dependent(delta_finish_kernel<float>, dim3(grid), dim3(128), 0, st, o, z, ldz, n_parts, part_stride, silu_gate, w, (float*)out, n_tokens, H, E, eps);
+        e = ub_launch_dependent(delta_finish_kernel<float>, dim3(grid), dim3(128), 0, st, o, z, ldz, n_parts, part_stride, silu_gate, w, (float*)out, n_tokens, H, E, eps, w_heads);
     else if (out_dtype == UB_BF16)
-        e = ub_launch_dependent(delta_finish_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, o, z, ldz, n_parts, part_stride, silu_gate, w, (__nv_bfloat16*)out, n_tokens, H, E, eps);
+        e = ub_launch_dependent(delta_finish_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, o, z, ldz, n_parts, part_stride, silu_gate, w, (__nv_bfloat16*)out, n_tokens, H, E, eps, w_heads);
     else return UB_ERR_UNSUPPORTED;
     return (int)e;
 }

@@ -16,6 +16,9 @@
 //             product that reads its rows in the sorted order (the tensor-core one: a tile is one TMA box).
 //   combine   one block a token: residual += sum_k w_k * (expert row k, or the token's own input for an
 //             identity expert), in the order of k.
+// ``mode`` (bits) and ``wscale`` choose another router of the same family: bit 0, s = sigmoid(z) instead of the softmax;
+// bit 1, a group's score is the sum of its two largest choice scores instead of the largest; bit 2, the chosen outputs'
+// weights are divided by their sum (+ 1e-20); the weights are then multiplied by ``wscale``.
 // Places within a segment are handed out by an atomic counter, so they differ from run to run; every row of a
 // product is computed on its own, so no result depends on them.
 #include "common.cuh"
@@ -28,7 +31,7 @@ constexpr int ROUTE_WARPS = 4;
 __device__ __forceinline__ void route_token(const float* __restrict__ zr, int n_parts, long long part_stride,
                                             const float* __restrict__ corr, int n_out, int n_experts, int top, int n_groups,
                                             int keep, float* sc, float* ch, float* gm, int lane, int* idx_t, float* wts_t,
-                                            int* counts) {
+                                            int* counts, int mode, float wscale) {
     float m = -INFINITY;
     for (int i = lane; i < n_out; i += 32) {              // the logits may come as K slices: summed in the slices' order
         float v = zr[i];
@@ -36,18 +39,25 @@ __device__ __forceinline__ void route_token(const float* __restrict__ zr, int n_
         sc[i] = v;
         m = fmaxf(m, v);
     }
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int i = lane; i < n_out; i += 32) { const float e = expf(sc[i] - m); sc[i] = e; sum += e; }
-    sum = warp_sum(sum);
-    for (int i = lane; i < n_out; i += 32) { const float s = sc[i] / sum; sc[i] = s; ch[i] = s + (corr ? corr[i] : 0.f); }
+    if (mode & 1) {
+        for (int i = lane; i < n_out; i += 32) { const float s = 1.0f / (1.0f + expf(-sc[i])); sc[i] = s; ch[i] = s + (corr ? corr[i] : 0.f); }
+    } else {
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int i = lane; i < n_out; i += 32) { const float e = expf(sc[i] - m); sc[i] = e; sum += e; }
+        sum = warp_sum(sum);
+        for (int i = lane; i < n_out; i += 32) { const float s = sc[i] / sum; sc[i] = s; ch[i] = s + (corr ? corr[i] : 0.f); }
+    }
     __syncwarp();
     if (n_groups > 1 && keep < n_groups) {
         const int size = n_out / n_groups;
         for (int g = lane; g < n_groups; g += 32) {
-            float b = -INFINITY;
-            for (int i = 0; i < size; ++i) b = fmaxf(b, ch[g * size + i]);
-            gm[g] = b;
+            float b = -INFINITY, b2 = -INFINITY;           // the largest and the second largest
+            for (int i = 0; i < size; ++i) {
+                const float v = ch[g * size + i];
+                if (v > b) { b2 = b; b = v; } else if (v > b2) b2 = v;
+            }
+            gm[g] = ((mode & 2) && size > 1) ? b + b2 : b;
         }
         __syncwarp();
         // the kept groups are marked with +inf; what is left unmarked loses its outputs
@@ -91,12 +101,21 @@ __device__ __forceinline__ void route_token(const float* __restrict__ zr, int n_
         }
         __syncwarp();
     }
+    if (lane == 0 && ((mode & 4) || wscale != 1.0f)) {
+        float f = wscale;
+        if (mode & 4) {
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) sum += wts_t[k];
+            f = wscale / (sum + 1e-20f);
+        }
+        for (int k = 0; k < top; ++k) wts_t[k] *= f;
+    }
 }
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long part_stride, const float* __restrict__ corr,
              int n_tokens, int n_out, int n_experts, int top, int n_groups, int keep, int* __restrict__ idx,
-             float* __restrict__ wts, int* __restrict__ counts) {
+             float* __restrict__ wts, int* __restrict__ counts, int mode, float wscale) {
     extern __shared__ float sm[];
     pdl_trigger();
     pdl_wait();
@@ -107,7 +126,7 @@ route_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long 
     float* ch = sc + n_out;                                      // choice scores
     float* gm = ch + n_out;                                      // a group's best choice score
     route_token(z + t * ldz, n_parts, part_stride, corr, n_out, n_experts, top, n_groups, keep, sc, ch, gm, lane,
-                idx + t * top, wts + t * top, counts);
+                idx + t * top, wts + t * top, counts, mode, wscale);
 }
 
 // route, plan and scatter of a step of few tokens in ONE block (the counters live in shared memory; the global ones are
@@ -118,7 +137,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32)
 route_small_kernel(const float* __restrict__ z, long long ldz, int n_parts, long long part_stride, const float* __restrict__ corr,
                    int n_tokens, int n_out, int n_experts, int top, int n_groups, int keep, int* __restrict__ idx,
                    float* __restrict__ wts, int4* __restrict__ tiles, int* __restrict__ n_tiles, int* __restrict__ row_pos,
-                   int* __restrict__ src_rows, int tile) {
+                   int* __restrict__ src_rows, int tile, int mode, float wscale) {
     extern __shared__ float sm[];
     pdl_trigger();
     pdl_wait();
@@ -133,7 +152,7 @@ route_small_kernel(const float* __restrict__ z, long long ldz, int n_parts, long
     float* sc = sm + (size_t)warp * per_warp;
     for (int t = warp; t < n_tokens; t += SMALL_WARPS) {
         route_token(z + (long long)t * ldz, n_parts, part_stride, corr, n_out, n_experts, top, n_groups, keep, sc, sc + n_out,
-                    sc + 2 * n_out, lane, idx + (long long)t * top, wts + (long long)t * top, cnt);
+                    sc + 2 * n_out, lane, idx + (long long)t * top, wts + (long long)t * top, cnt, mode, wscale);
         __syncwarp();
     }
     __syncthreads();
@@ -267,7 +286,7 @@ __global__ void combine_vec_kernel(const TY* __restrict__ y, const TH* __restric
 // whose sum they are.
 UB_API int ub_route(const float* z, long long ldz, int n_parts, long long part_stride, const float* corr, int n_tokens,
                     int n_out, int n_experts, int top, int n_groups, int keep, int* idx, float* wts, int* counts,
-                    cudaStream_t st) {
+                    int mode, float wscale, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (n_parts < 1) return UB_ERR_ARG;
     if (n_out < 1 || n_experts < 0 || n_experts > n_out || top < 1 || top > n_out || n_groups < 1 || n_out % n_groups ||
@@ -276,7 +295,7 @@ UB_API int ub_route(const float* z, long long ldz, int n_parts, long long part_s
     if (smem > 48 * 1024) return UB_ERR_ARG;
     const unsigned grid = (unsigned)((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS);
     return (int)ub_launch_dependent(route_kernel, dim3(grid), dim3(ROUTE_WARPS * 32), smem, st, z, ldz, n_parts, part_stride, corr,
-                                    n_tokens, n_out, n_experts, top, n_groups, keep, idx, wts, counts);
+                                    n_tokens, n_out, n_experts, top, n_groups, keep, idx, wts, counts, mode, wscale);
 }
 
 // The three steps above in one launch, for steps of at most ROUTE_SMALL_TOKENS tokens.
@@ -285,7 +304,7 @@ UB_API int ub_route_small_tokens() { return ROUTE_SMALL_TOKENS; }
 
 UB_API int ub_route_small(const float* z, long long ldz, int n_parts, long long part_stride, const float* corr, int n_tokens,
                           int n_out, int n_experts, int top, int n_groups, int keep, int* idx, float* wts, void* tiles,
-                          int* n_tiles, int* row_pos, int* src_rows, int tile, cudaStream_t st) {
+                          int* n_tiles, int* row_pos, int* src_rows, int tile, int mode, float wscale, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (n_parts < 1 || n_tokens > ROUTE_SMALL_TOKENS || tile < 1) return UB_ERR_ARG;
     if (n_out < 1 || n_experts < 1 || n_experts > n_out || top < 1 || top > n_out || n_groups < 1 || n_out % n_groups ||
@@ -294,7 +313,7 @@ UB_API int ub_route_small(const float* z, long long ldz, int n_parts, long long 
     if (smem > 48 * 1024) return UB_ERR_ARG;
     return (int)ub_launch_dependent(route_small_kernel, dim3(1), dim3(SMALL_WARPS * 32), smem, st, z, ldz, n_parts, part_stride,
                                     corr, n_tokens, n_out, n_experts, top, n_groups, keep, idx, wts, (int4*)tiles, n_tiles,
-                                    row_pos, src_rows, tile);
+                                    row_pos, src_rows, tile, mode, wscale);
 }
 
 UB_API int ub_route_plan(int* counts, int* cursor, int* seg_start, void* tiles, int* n_tiles, int n_experts, int tile,

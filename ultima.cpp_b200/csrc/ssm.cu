@@ -421,3 +421,87 @@ UB_API int ub_ssm_finish(const float* y, const float* p, long long ldp, int n_pa
     else return UB_ERR_UNSUPPORTED;
     return (int)e;
 }
+
+// ---------------------------------------------------------------------------------------
+// The selective scan with a decay for every (channel, state element) (the first Mamba form).  For channel c with the step
+// size dt = softplus(dtp + dt_bias[c]), the input x (convolved, activated), and the token's B and C rows of N numbers:
+//     S[c, n] <- exp(dt A[c, n]) S[c, n] + dt x B[n];    y = sum_n S[c, n] C[n] + D[c] x;    out = y * silu(z)
+// A = -exp(A_log) is made once at load.  Four lanes hold one channel's N state elements (NR = ceil(N / 4) each, element
+// n with lane n % 4), tokens are taken in order, a channel's state stays in registers for the step.  Everything is float32;
+// x comes in the activation type (it is a convolution's output), z as float32 sums of the input product's K slices.
+// ---------------------------------------------------------------------------------------
+template <typename TX, typename TO, int NR>
+__global__ void __launch_bounds__(128)
+mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, const float* __restrict__ dt_bias,
+                   const float* __restrict__ bc, long long ldbc, int b_off, int c_off, const float* __restrict__ A,
+                   const float* __restrict__ Dskip, const float* __restrict__ z, long long ldz, int z_parts, long long z_part_stride,
+                   TO* __restrict__ out, float* __restrict__ S, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                   int inner, int N) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 2, q = threadIdx.x & 3;
+    const int t0 = seq_start[b], t1 = seq_start[b + 1];
+    if (c >= inner || t0 >= t1) return;                    // (the four lanes of a channel leave together)
+    const unsigned lanes = __activemask();
+    float* Sc = S + ((long long)seq_slot[b] * inner + c) * N;
+    float s[NR], a[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int n = i * 4 + q;
+        s[i] = n < N ? Sc[n] : 0.f;
+        a[i] = n < N ? A[(long long)c * N + n] : 0.f;
+    }
+    const float bias = dt_bias[c], dsk = Dskip[c];
+    for (long long t = t0; t < t1; ++t) {
+        const float pre = dtp[t * inner + c] + bias;
+        const float dt = pre > 20.f ? pre : log1pf(expf(pre));
+        const float xv = to_f32<TX>(x[t * inner + c]);
+        const float dx = dt * xv;
+        const float* Bt = bc + t * ldbc + b_off;
+        const float* Ct = bc + t * ldbc + c_off;
+        float y = 0.f;
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int n = i * 4 + q;
+            if (n < N) {
+                s[i] = fmaf(expf(dt * a[i]), s[i], dx * Bt[n]);
+                y = fmaf(s[i], Ct[n], y);
+            }
+        }
+        y += __shfl_xor_sync(lanes, y, 1);
+        y += __shfl_xor_sync(lanes, y, 2);
+        if (q == 0) {
+            float zv = 0.f;
+            for (int i = 0; i < z_parts; ++i) zv += z[i * z_part_stride + t * ldz + c];
+            y = fmaf(dsk, xv, y);
+            out[t * inner + c] = from_f32<TO>(y * zv / (1.0f + expf(-zv)));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int n = i * 4 + q;
+        if (n < N) Sc[n] = s[i];
+    }
+}
+
+UB_API int ub_mamba1_scan(const void* x, int x_dtype, const float* dtp, const float* dt_bias, const float* bc, long long ldbc,
+                          int b_off, int c_off, const float* A, const float* Dskip, const float* z, long long ldz, int z_parts,
+                          long long z_part_stride, void* out, int out_dtype, float* S, const int* seq_start, const int* seq_slot,
+                          int n_seqs, int n_tokens, int inner, int N, cudaStream_t st) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (inner <= 0 || N <= 0 || N > 256 || n_seqs > 65535 || z_parts < 1 || x_dtype != out_dtype) return UB_ERR_ARG;
+    const dim3 grid((unsigned)((inner * 4 + 127) / 128), n_seqs), block(128);
+    const int nr = (N + 3) / 4;
+    // a step of more than one token a sequence starts behind the end of the kernels before it (its blocks are busy for the
+    // whole step and should each find a multiprocessor with room), as the other scans do
+    const bool dep = n_tokens <= n_seqs;
+    cudaError_t e = cudaErrorInvalidValue;
+#define GO3(TX, NRR) e = ub_launch_ordered(dep, mamba1_scan_kernel<TX, TX, NRR>, grid, block, 0, st, (const TX*)x, dtp, dt_bias, bc, ldbc, b_off, \
+                                           c_off, A, Dskip, z, ldz, z_parts, z_part_stride, (TX*)out, S, seq_start, seq_slot, inner, N)
+#define GO(NRR) do { if (x_dtype == UB_F32) GO3(float, NRR); else if (x_dtype == UB_BF16) GO3(__nv_bfloat16, NRR); else return UB_ERR_UNSUPPORTED; } while (0)
+    if (nr <= 2) GO(2); else if (nr <= 4) GO(4); else if (nr <= 8) GO(8); else if (nr <= 16) GO(16); else if (nr <= 32) GO(32); else GO(64);
+#undef GO
+#undef GO3
+    return (int)e;
+}

@@ -16,7 +16,7 @@ TRACE = os.environ.get("ULTIMA_TRACE", "") not in ("", "0")
 def _trace(name: str, index: int, x: torch.Tensor) -> None:
     print(f"{name}-{index} = {{{x.numel()}}} sum = {x.double().sum().item():.6f}", file=sys.stderr, flush=True)
 
-from ..parts.base import ModelSpec, build_part
+from ..parts.base import KVNeed, ModelSpec, StateNeed, build_part
 
 
 class BuiltLayer:
@@ -27,14 +27,38 @@ class BuiltLayer:
         self.arrangement, self.parts = arrangement, dict(parts)
         for role, p in parts.items():
             setattr(self, role, p)
-        holders = [p for p in parts.values() if getattr(p, "cache_need", None) is not None and p.cache_need() is not None]
-        if len(holders) > 1:
-            raise ValueError("a layer may hold one part that keeps a cache; this one has "
-                             + ", ".join(f"{p.family} '{p.kind}'" for p in holders))
-        self.cache_holder = holders[0] if holders else None
+        holders = [(role, p) for role, p in parts.items()
+                   if getattr(p, "cache_need", None) is not None and p.cache_need() is not None]
+        if len(holders) > 1 and not getattr(arrangement, "shares_cache", False):
+            raise ValueError("a layer of this arrangement may hold one part that keeps a cache; this one has "
+                             + ", ".join(f"{p.family} '{p.kind}'" for _, p in holders))
+        self.cache_holder = holders[0][1] if holders else None
+        # several holders (an arrangement that says ``shares_cache``): the run's need is all of theirs in the order of the
+        # roles, and ``cache_of`` hands a part its share
+        self._needs = {role: (n if isinstance(n, tuple) else (n,)) for role, p in holders for n in (p.cache_need(),)}
+        if sum(isinstance(n, KVNeed) for ns in self._needs.values() for n in ns) > 1:
+            raise ValueError("a layer may keep one set of keys and values")
 
     def cache_need(self):
-        return self.cache_holder.cache_need() if self.cache_holder is not None else None
+        if len(self._needs) <= 1:
+            return self.cache_holder.cache_need() if self.cache_holder is not None else None
+        return tuple(n for ns in self._needs.values() for n in ns)
+
+    def cache_of(self, role: str, cache):
+        """The part of the run's cache that belongs to the part in ``role`` (None if it keeps nothing)."""
+        mine = self._needs.get(role)
+        if cache is None or mine is None:
+            return None
+        if len(self._needs) == 1:
+            return cache
+        before = 0
+        for r, ns in self._needs.items():
+            if r == role:
+                break
+            before += sum(isinstance(n, StateNeed) for n in ns)
+        states = tuple(cache.states[before:before + sum(isinstance(n, StateNeed) for n in mine)])
+        kv = cache.kv if any(isinstance(n, KVNeed) for n in mine) else None
+        return type(cache)(kv=kv, state=states[0] if states else None, owner=cache.owner, states=states)
 
     @property
     def graph_safe(self) -> bool:

@@ -83,6 +83,8 @@ class Runtime:
         self.cache_dtype = dtype
         self.arena = Arena(self.device)
         self._shared: dict = {}
+        self._carry: dict = {}
+        self._carry_retired: list = []
         self.use_tensor_cores = dtype == torch.bfloat16
         self.launches = 0              # kernels of this library launched through the runtime
         self.pass_id = 0               # counts the passes through the layers (Model.forward); what an arrangement
@@ -98,6 +100,18 @@ class Runtime:
         if key not in self._shared:
             self._shared[key] = make()
         return self._shared[key]
+
+    def carry(self, key, rows: int, cols: int, dtype):
+        """A [rows, cols] array that one part of a pass fills and a later part of the same pass reads.  It lives outside the
+        arena (which layers reset) at an address that stays the same from step to step, so a captured step may use it;
+        when it has to grow, the old storage is kept alive for the graphs that point into it."""
+        held = self._carry.get(key)
+        n = int(rows) * int(cols)
+        if held is None or held.dtype != dtype or held.numel() < n:
+            if held is not None:
+                self._carry_retired.append(held)
+            held = self._carry[key] = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+        return held[:n].view(int(rows), int(cols))
 
     def check_status(self) -> None:
         """Read the flags the kernels raise (one small copy; waits for the stream)."""

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 PLAIN = [("basic.cu", ()), ("gemm_simt.cu", ()), ("attn_simple.cu", ()), ("sampling.cu", ()),
          ("gemm_tcgen05.cu", ()), ("delta.cu", ()), ("ssm.cu", ()),
-         ("streams.cu", ()), ("latent.cu", ()), ("routed.cu", ())]
+         ("streams.cu", ()), ("latent.cu", ()), ("routed.cu", ()), ("rowwise.cu", ())]
 # the tensor-core attention library is built for each head size; these are the sizes that the
 # tests, the bench and the usual checkpoints use (any other multiple of 16 is built on demand)
 HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128, 256)

@@ -119,10 +119,10 @@ def _declare(lib, source: str) -> None:
                          "ub_gemm_simt_grouped": [P, I, P, P, I, P, I, I, I, L, L, L, L, P, P, P, I, I, P]},
         "streams.cu": {"ub_streams_fill": [P, P, I, I, I, P],
                        "ub_streams_pass": [P, L, I, P, P, P, P, I, P, P, P, I, I, I, F, P]},
-        "routed.cu": {"ub_route": [P, L, I, L, P, I, I, I, I, I, I, P, P, P, P],
+        "routed.cu": {"ub_route": [P, L, I, L, P, I, I, I, I, I, I, P, P, P, I, F, P],
                       "ub_route_plan": [P, P, P, P, P, I, I, P],
                       "ub_route_scatter": [P, P, P, P, P, I, I, I, P],
-                      "ub_route_small": [P, L, I, L, P, I, I, I, I, I, I, P, P, P, P, P, P, I, P],
+                      "ub_route_small": [P, L, I, L, P, I, I, I, I, I, I, P, P, P, P, P, P, I, I, F, P],
                       "ub_route_combine": [P, I, P, I, P, P, P, I, I, I, P],
                       "ub_route_gather": [P, P, P, I, I, L, P]},
         "latent.cu": {"ub_latent_place": [P, I, L, I, L, I, I, P, P, I, P, P, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P]},
@@ -133,12 +133,21 @@ def _declare(lib, source: str) -> None:
                                             I, I, I, F, I, P, P]},
         "delta.cu": {"ub_delta_prepare": [P, L, I, L, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
                      "ub_conv_state_update": [P, L, I, L, P, P, P, I, I, I, P],
-                     "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
-                     "ub_delta_finish": [P, P, L, I, L, I, P, P, I, I, I, I, F, P]},
+                     "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P, P],
+                     "ub_delta_finish": [P, P, L, I, L, I, P, P, I, I, I, I, F, I, P],
+                     "ub_gdelta_prepare": [P, L, I, L, I, I, I, I, P, P, P, P, P, P, P, P, P, I, I, I, F, F, P]},
         "ssm.cu": {"ub_ssm_prepare": [P, L, I, L, P, P, P, P, I, P, P, P, P, P, P, P, P, I, P],
                    "ub_ssm_conv_state_update": [P, L, I, L, P, P, P, P, I, P],
                    "ub_ssm_scan": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
-                   "ub_ssm_finish": [P, P, L, I, L, P, P, P, I, I, I, F, F, P]},
+                   "ub_ssm_finish": [P, P, L, I, L, P, P, P, I, I, I, F, F, P],
+                   "ub_mamba1_scan": [P, I, P, P, P, L, I, I, P, P, P, L, I, L, P, I, P, P, P, I, I, I, I, P]},
+        "rowwise.cu": {"ub_layernorm": [P, P, P, I, P, I, I, F, P],
+                       "ub_scale_add_norm": [P, P, P, I, P, F, P, I, I, I, I, P],
+                       "ub_causal_conv": [P, I, L, I, L, I, P, P, P, P, P, P, P, I, L, I, I, I, I, I, I, I, I, P, P, P, P],
+                       "ub_causal_conv_state": [P, I, L, I, L, I, P, P, P, P, I, I, I, P],
+                       "ub_take_cols": [P, L, I, L, I, I, I, P, I, L, I, I, P],
+                       "ub_unary": [P, I, P, I, L, I, P],
+                       "ub_side_gate": [P, L, P, I, L, I, P, I, P, I, L, I, I, I, P]},
         "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P, P, I, P], "ub_sample_params_size": []},
     }.get(source, {})
     for name, args in sigs.items():
@@ -551,9 +560,12 @@ def gemm_grouped(a, w, out, tiles, n_tiles, src_rows, max_tiles, epilogue=EPI_ST
 ROUTE_TILE = 64          # sorted rows a tile of the grouped products
 
 
-def route(z, correction, n_experts, top, n_groups, keep, idx, wts, counts):
+ROUTE_SIGMOID, ROUTE_GROUP_TOP2, ROUTE_NORMALISE = 1, 2, 4      # bits of a router's ``mode`` (csrc/routed.cu)
+
+
+def route(z, correction, n_experts, top, n_groups, keep, idx, wts, counts, mode=0, wscale=1.0):
     """z float32 [T, outputs] router logits (or [parts, T, outputs], summed in that order) -> idx int32 [T, top], wts
-    float32 [T, top]; counts int32 [n_experts] += rows."""
+    float32 [T, top]; counts int32 [n_experts] += rows.  ``mode``: ROUTE_* bits; ``wscale`` multiplies the weights."""
     _need_cuda(z, correction, idx, wts, counts)
     T, ldz, n_parts, part_stride = _parts_of(z)
     n_out = z.shape[-1]
@@ -561,13 +573,14 @@ def route(z, correction, n_experts, top, n_groups, keep, idx, wts, counts):
     assert idx.is_contiguous() and wts.is_contiguous() and idx.shape == wts.shape == (T, top) and counts.dtype == torch.int32
     assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == n_out)
     _check(_lib("routed.cu").ub_route(_ptr(z), ldz, n_parts, part_stride, _ptr(correction), T, n_out, n_experts, top, n_groups, keep,
-                                      _ptr(idx), _ptr(wts), _ptr(counts), _stream()), "route")
+                                      _ptr(idx), _ptr(wts), _ptr(counts), int(mode), float(wscale), _stream()), "route")
 
 
 ROUTE_SMALL_TOKENS = 16      # steps of at most this many tokens (a warp each): route, plan and scatter as one launch (csrc/routed.cu)
 
 
-def route_small(z, correction, n_experts, top, n_groups, keep, idx, wts, tiles, n_tiles, row_pos, src_rows, tile):
+def route_small(z, correction, n_experts, top, n_groups, keep, idx, wts, tiles, n_tiles, row_pos, src_rows, tile, mode=0,
+                wscale=1.0):
     """``route``, ``route_plan`` and ``route_scatter`` of a step of at most ROUTE_SMALL_TOKENS tokens in one launch of one
     block; the counters of the separate kernels are not used."""
     _need_cuda(z, correction, idx, wts, tiles, n_tiles, row_pos, src_rows)
@@ -581,7 +594,7 @@ def route_small(z, correction, n_experts, top, n_groups, keep, idx, wts, tiles, 
     assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == n_out)
     _check(_lib("routed.cu").ub_route_small(_ptr(z), ldz, n_parts, part_stride, _ptr(correction), T, n_out, n_experts, top,
                                             n_groups, keep, _ptr(idx), _ptr(wts), _ptr(tiles), _ptr(n_tiles), _ptr(row_pos),
-                                            _ptr(src_rows), tile, _stream()), "route_small")
+                                            _ptr(src_rows), tile, int(mode), float(wscale), _stream()), "route_small")
 
 
 def route_plan(counts, cursor, seg_start, tiles, n_tiles, n_experts, tile=ROUTE_TILE):
@@ -743,28 +756,178 @@ def conv_state_update(p, conv_state, batch, n_channels, taps):
                                                  taps, _stream()), "conv_state_update")
 
 
-def delta_scan(qn, kn, vc, beta, dec, out, state, batch, H, G, D, E):
-    _need_cuda(qn, kn, vc, beta, dec, out, state)
+def delta_scan(qn, kn, vc, beta, dec, out, state, batch, H, G, D, E, rem=None, kraw=None):
+    """``rem`` and ``kraw`` (both or neither, float32 of the keys' shape): the generalised rule, S[d, :] = dec[d] S[d, :]
+    - rem[d] (S^T kn) + kraw[d] v with both terms reading the old state; ``beta`` is then not read."""
+    _need_cuda(qn, kn, vc, beta, dec, out, state, rem, kraw)
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, D, E)
+    assert (rem is None) == (kraw is None)
+    for t in (rem, kraw):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.shape == kn.shape)
     _check(_lib("delta.cu").ub_delta_scan(_ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(dec), _ptr(out), _ptr(state),
                                           _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, qn.shape[0], H, G, D, E, sm_count(),
-                                          _stream()),
+                                          _ptr(rem), _ptr(kraw), _stream()),
            "delta_scan")
+
+
+def gdelta_prepare(p, offs, a_bias, wpre, w0, rn, un, kraw, rem, dec, vc, H, D, unit_eps, decay_scale):
+    """The generalised delta rule's operands from the projection row p (float32 [T, N] or [parts, T, N]; ``offs`` the first
+    columns of r, k, v and the removal rate's sums) and the decay's sums ``wpre`` [T, H * D]: see csrc/delta.cu."""
+    _need_cuda(p, a_bias, wpre, w0, rn, un, kraw, rem, dec, vc)
+    assert p.dtype == torch.float32
+    T, ldp, n_parts, part_stride = _parts_of(p)
+    for t in (a_bias, wpre, w0, rn, un, kraw, rem, dec, vc):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    _check(_lib("delta.cu").ub_gdelta_prepare(_ptr(p), ldp, n_parts, part_stride, int(offs[0]), int(offs[1]), int(offs[2]),
+                                              int(offs[3]), _ptr(a_bias), _ptr(wpre), _ptr(w0), _ptr(rn), _ptr(un), _ptr(kraw),
+                                              _ptr(rem), _ptr(dec), _ptr(vc), T, H, D, float(unit_eps), float(decay_scale),
+                                              _stream()), "gdelta_prepare")
 
 
 def delta_finish(o, gate_pre, weight, out, H, E, eps, silu_gate=False):
     """out = o / rms(o) * weight * sigmoid(gate_pre) (``silu_gate``: * silu(gate_pre)), head by head; o float32
-    [T, H * E]; gate_pre float32 [T, H * E] or [parts, T, H * E] (summed), rows of any stride."""
+    [T, H * E]; gate_pre float32 [T, H * E] or [parts, T, H * E] (summed), rows of any stride.  ``weight``: [E], shared
+    by the heads, or [H * E], a weight for every head."""
     _need_cuda(o, gate_pre, weight, out)
     assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
     assert gate_pre.dtype == torch.float32 and gate_pre.shape[-2:] == o.shape
     _, ldz, n_parts, part_stride = _parts_of(gate_pre)
     _check(_lib("delta.cu").ub_delta_finish(_ptr(o), _ptr(gate_pre), ldz, n_parts, part_stride, 1 if silu_gate else 0,
-                                            _ptr(weight), _ptr(out), _code(out), o.shape[0], H, E, float(eps), _stream()),
+                                            _ptr(weight), _ptr(out), _code(out), o.shape[0], H, E, float(eps),
+                                            1 if (weight.numel() == H * E and H > 1) else 0, _stream()),
            "delta_finish")
 
 
 # ---------------------------------------------------------------------------------------
+# ---------------------------------------------------------------------------------------
+# row-wise kernels of a stream with scaled sublayers and input convolutions (csrc/rowwise.cu)
+def layernorm(x, weight, out, eps, rows=None):
+    """out = (x - mean) / sqrt(var + eps) * weight row by row (no bias); x float32 [T, width]; ``rows`` int32: only these."""
+    _need_cuda(x, weight, out, rows)
+    width = x.shape[1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[1] == width
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == width
+    n = x.shape[0] if rows is None else rows.numel()
+    assert out.shape[0] == n
+    _check(_lib("rowwise.cu").ub_layernorm(_ptr(x), _ptr(weight), _ptr(out), _code(out), _ptr(rows), n, width, float(eps),
+                                           _stream()), "layernorm")
+
+
+NEXT_NONE, NEXT_PLAIN, NEXT_RMS, NEXT_LAYER = 0, 1, 2, 3
+
+
+def scale_add_norm(y, scale, x, mode=NEXT_NONE, norm_weight=None, eps=0.0, out=None, clear_y=True):
+    """x += scale * y (``scale`` float32 [width] or None for 1), y cleared; ``out`` receives what the next sublayer reads:
+    the new x as it is (NEXT_PLAIN), its RMS norm (NEXT_RMS) or its layer norm (NEXT_LAYER) times ``norm_weight``."""
+    _need_cuda(y, scale, x, norm_weight, out)
+    T, width = x.shape
+    assert x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+    for v in (scale, norm_weight):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == width)
+    assert out is None or (out.is_contiguous() and tuple(out.shape) == (T, width))
+    _check(_lib("rowwise.cu").ub_scale_add_norm(_ptr(y), _ptr(scale), _ptr(x), int(mode), _ptr(norm_weight), float(eps), _ptr(out),
+                                                _code(out) if out is not None else F32, T, width, 1 if clear_y else 0, _stream()),
+           "scale_add_norm")
+
+
+def _conv_in(x, col_off, n_cols):
+    if x.dim() == 3:
+        assert x.stride(2) == 1 and col_off + n_cols <= x.shape[2]
+        return x.shape[1], x.stride(1), x.shape[0], x.stride(0)
+    assert x.stride(1) == 1 and col_off + n_cols <= x.shape[1]
+    return x.shape[0], x.stride(0), 1, 0
+
+
+def causal_conv(x, w, state, batch, out, col_off=0, bias=None, add_input=False, silu=False, mix=None, out_bias=None):
+    """A short causal convolution over time on ``C = out.shape[1]`` channels of x (columns from ``col_off`` on; x [T, N] or
+    [parts, T, N], summed; ``bias`` [C] is added to every input first): out_t = sum_j w[:, j] u_(t - taps + 1 + j), with the
+    inputs of before the step from ``state`` float32 [slots, taps - 1, C] and zeros before a sequence's start.  ``w`` None:
+    no convolution (out = u).  ``add_input``: out = u + conv(u).  ``out_bias`` [C]: added to the result (a bias of the
+    convolution, which the state does not hold).  ``silu``: through SiLU.  ``mix`` = (mode, lo, hi, lam,
+    shared): the channels lo .. hi - 1 go out to ``shared`` float32 [T, hi - lo] (mode 1) or become (1 - lam) * own +
+    lam * shared (mode 2; lam a float32 scalar on the device).  The state is not moved on: ``causal_conv_state`` does that."""
+    _need_cuda(x, w, state, out, bias, out_bias)
+    assert out_bias is None or (out_bias.dtype == torch.float32 and out_bias.is_contiguous() and out_bias.numel() == out.shape[1])
+    C = out.shape[1]
+    T, ldx, n_parts, part_stride = _conv_in(x, col_off, C)
+    taps = 0 if w is None else w.shape[1]
+    assert out.shape[0] == T and out.stride(1) == 1
+    assert w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == C)
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C)
+    if taps > 1:
+        assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, C)
+    mode, lo, hi, lam, shared = mix if mix is not None else (0, 0, 0, None, None)
+    if mode:
+        _need_cuda(lam, shared)
+        assert shared.dtype == torch.float32 and shared.is_contiguous() and tuple(shared.shape) == (T, hi - lo)
+        assert lam is None or (lam.dtype == torch.float32 and lam.numel() == 1)
+    _check(_lib("rowwise.cu").ub_causal_conv(
+        _ptr(x), _code(x), ldx, n_parts, part_stride, int(col_off), _ptr(bias), _ptr(w), _ptr(state) if taps > 1 else 0,
+        _ptr(batch.tok_seq), _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(out), _code(out), out.stride(0), T, C, taps,
+        1 if add_input else 0, 1 if silu else 0, int(mode), int(lo), int(hi), _ptr(lam), _ptr(shared), _ptr(out_bias),
+        _stream()), "causal_conv")
+
+
+def causal_conv_state(x, state, batch, col_off=0, bias=None):
+    """The last taps - 1 inputs of (state ++ the step's inputs) become the state; x, col_off and bias as ``causal_conv`` got them."""
+    _need_cuda(x, state, bias)
+    K, C = state.shape[1], state.shape[2]
+    _, ldx, n_parts, part_stride = _conv_in(x, col_off, C)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    _check(_lib("rowwise.cu").ub_causal_conv_state(_ptr(x), _code(x), ldx, n_parts, part_stride, int(col_off), _ptr(bias),
+                                                   _ptr(state), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, C,
+                                                   K + 1, _stream()), "causal_conv_state")
+
+
+def take_cols(x, col_off, n, out, tanh=False):
+    """out[:, :n] = x[:, col_off : col_off + n] (x float32 [T, N] or [parts, T, N], summed), through tanh if asked; the
+    columns of ``out`` from n on are zeroed (an operand padded to an aligned width)."""
+    _need_cuda(x, out)
+    assert x.dtype == torch.float32 and out.stride(1) == 1 and n <= out.shape[1]
+    T, ldx, n_parts, part_stride = _conv_in(x, col_off, n)
+    assert out.shape[0] == T
+    _check(_lib("rowwise.cu").ub_take_cols(_ptr(x), ldx, n_parts, part_stride, int(col_off), int(n), 1 if tanh else 0, _ptr(out),
+                                           _code(out), out.stride(0), out.shape[1], T, _stream()), "take_cols")
+
+
+UNARY_GELU_ERF, UNARY_RELU_SQUARED = 1, 2
+
+
+def unary(x, out, kind):
+    _need_cuda(x, out)
+    assert x.is_contiguous() and out.is_contiguous() and x.shape == out.shape
+    _check(_lib("rowwise.cu").ub_unary(_ptr(x), _code(x), _ptr(out), _code(out), x.numel(), int(kind), _stream()), "unary")
+
+
+def side_gate(s, table, col0, ids, out, dim):
+    """out[t, j] = gelu_tanh(s[t, j]) * table[ids[t], col0 + j] for j < dim, zero beyond; s float32 [T, >= dim]."""
+    _need_cuda(s, table, ids, out)
+    assert s.dtype == torch.float32 and s.stride(1) == 1 and table.stride(1) == 1 and out.stride(1) == 1
+    assert ids.dtype == torch.int32 and col0 + dim <= table.shape[1] and dim <= out.shape[1] and dim <= s.shape[1]
+    _check(_lib("rowwise.cu").ub_side_gate(_ptr(s), s.stride(0), _ptr(table), _code(table), table.stride(0), int(col0), _ptr(ids),
+                                           table.shape[0], _ptr(out), _code(out), out.stride(0), int(dim), out.shape[1],
+                                           s.shape[0], _stream()), "side_gate")
+
+
+def mamba1_scan(x, dtp, dt_bias, bc, b_off, c_off, A, d_skip, z, out, state, batch, N):
+    """The selective scan with a decay for every (channel, state element); see csrc/ssm.cu.  x, out [T, inner] in the
+    activation type; dtp float32 [T, inner] (the step size's sums before the bias); bc float32 [T, >= c_off + N] with the B
+    row from column b_off and the C row from c_off; A float32 [inner, N] (negative); z float32 [T, M] or [parts, T, M] whose
+    first ``inner`` columns are the gate's sums; state float32 [slots, inner, N]."""
+    _need_cuda(x, dtp, dt_bias, bc, A, d_skip, z, out, state)
+    T, inner = x.shape
+    assert x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and x.dtype == out.dtype
+    for t in (dtp, dt_bias, A, d_skip, state):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    assert bc.dtype == torch.float32 and bc.stride(1) == 1 and z.dtype == torch.float32
+    assert tuple(state.shape[1:]) == (inner, N) and tuple(A.shape) == (inner, N) and tuple(dtp.shape) == (T, inner)
+    _, ldz, z_parts, z_stride = _conv_in(z, 0, inner)
+    _check(_lib("ssm.cu").ub_mamba1_scan(_ptr(x), _code(x), _ptr(dtp), _ptr(dt_bias), _ptr(bc), bc.stride(0), int(b_off), int(c_off),
+                                         _ptr(A), _ptr(d_skip), _ptr(z), ldz, z_parts, z_stride, _ptr(out), _code(out), _ptr(state),
+                                         _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, T, inner, int(N), _stream()),
+           "mamba1_scan")
+
+
 SAMPLE_DTYPE = np.dtype([
     ("temperature", "<f4"), ("top_p", "<f4"), ("min_p", "<f4"), ("rep_penalty", "<f4"),
     ("freq_penalty", "<f4"), ("presence_penalty", "<f4"), ("dry_multiplier", "<f4"),

@@ -1,9 +1,9 @@
 """Parts a layer is put together from, and the description of a model as data."""
 from .base import (PartSpec, part, register_part, part_class, build_part, Part, Norm, Position, Rotation,
-                   Mixer, FeedForward, Arrangement, ResidualGate, Entry, Connection, KVNeed, StateNeed, LayerSpec, layer, Run, ModelSpec, FAMILIES)
+                   Mixer, FeedForward, Arrangement, ResidualGate, Entry, Connection, InputFilter, Tail, KVNeed, StateNeed, LayerSpec, layer, Run, ModelSpec, FAMILIES)
 from . import (norm, position, attention, delta, ssm, parallel, mlp, arrangement, embedding, connection, latent,
-               routed)   # registers the parts
+               routed, filtered)   # registers the parts
 
 __all__ = ["PartSpec", "part", "register_part", "part_class", "build_part", "Part", "Norm",
-           "Position", "Rotation", "Mixer", "FeedForward", "Arrangement", "ResidualGate", "Entry", "Connection", "KVNeed", "StateNeed",
+           "Position", "Rotation", "Mixer", "FeedForward", "Arrangement", "ResidualGate", "Entry", "Connection", "InputFilter", "Tail", "KVNeed", "StateNeed",
            "LayerSpec", "layer", "Run", "ModelSpec", "FAMILIES"]

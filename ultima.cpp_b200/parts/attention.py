@@ -9,7 +9,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.spec import WeightSpec
-from .base import Mixer, KVNeed, PartSpec, build_part, register_part
+from .base import Mixer, KVNeed, PartSpec, StateNeed, build_part, register_part
 
 
 @register_part("mixer", "attention")
@@ -47,6 +47,16 @@ class Attention(Mixer):
                   rel[bucket(n), h] to the score (behind scale and cap): bucket(n) = n below B // 2, beyond that
                   min(B - 1, B // 2 + floor(ln(n / (B // 2)) / ln(D / (B // 2)) * (B - B // 2))), equal steps of ln(n) up to D
       learned_sink   the sink's term is exp(sink[h]) with a learned number a head (tensor ``sink`` [heads]) instead of exp(0)
+      in_bias     the q, k and v projections have biases (tensors ``q_proj.bias`` ...), added to the projection's sums
+      conv        taps of a short causal convolution over time on every channel of q, k and v (tensors ``q_conv.weight``
+                  [channels, taps] ..., no bias, the last tap on the current token, zeros before the sequence), directly behind
+                  the projection and its bias, before norm and rotation; the last taps - 1 projected rows are per-sequence
+                  state (float32), so the layer then asks the cache for keys, values AND a state
+      value_mix   "source": the layer's values (behind the convolution) are also handed to the later layers of the pass that
+                  say "blend"; those replace their own by (1 - lam) * own + lam * the source's values of the same token (tensor
+                  ``vmix``, a scalar) before they are cached.  ``value_mix_key`` tells groups of such layers apart.  Both
+                  layers' value rows must have the same width.
+    The last three run as one kernel between the projection and the placement (csrc/rowwise.cu).
     With any of them the layer runs on the general kernels (csrc/attn_simple.cu: placement of q, k, v from
     one fused projection row [q | k | v | gate], attention with the mask and the gate inside); a block
     mask alone, with equal head sizes, still takes the tensor-core attention kernels.
@@ -64,7 +74,8 @@ class Attention(Mixer):
                  head_gate: bool = False, own_kv: bool = True, norm_whole: bool = False, keep_first: int = 0,
                  distance_slope: float | None = None, sink: bool = False, values_are_keys: bool = False,
                  wide_gate: bool = False, out_scale: float = 1.0, softcap: float | None = None,
-                 distance_buckets: tuple | None = None, learned_sink: bool = False):
+                 distance_buckets: tuple | None = None, learned_sink: bool = False, in_bias: bool = False, conv: int = 0,
+                 value_mix: str | None = None, value_mix_key: str = ""):
         if n_heads % n_kv_heads:
             raise ValueError("heads must be a multiple of kv heads")
         self.width, self.nh, self.nkv, self.hd = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
@@ -105,9 +116,21 @@ class Attention(Mixer):
                          or self.values_are_keys or self.wide_gate or self.out_scale != 1.0 or self.softcap is not None
                          or self.distance_buckets is not None)
         self._table_options = self.softcap is not None or self.distance_buckets is not None or self.learned_sink
-        self.place_rows = self.norm_whole or self.values_are_keys or self.wide_gate or (self.extended and interleaved)
+        self.in_bias, self.conv = bool(in_bias), int(conv or 0)
+        self.value_mix, self.value_mix_key = value_mix, str(value_mix_key)
+        if value_mix not in (None, "source", "blend"):
+            raise ValueError("attention: value_mix is 'source', 'blend' or None")
+        if not (0 <= self.conv <= 16):
+            raise ValueError(f"attention: a convolution of {self.conv} taps is not one the kernel takes (at most 16)")
+        # projections that are reshaped (bias, convolution, blended values) before they are placed
+        self.shaped = self.in_bias or self.conv > 0 or self.value_mix is not None
+        if self.shaped and (self.head_gate or self.wide_gate or self.values_are_keys or not self.own_kv):
+            raise ValueError("attention: biases, a convolution and blended values go with plain q, k and v projections of the "
+                             "layer's own")
+        self.place_rows = (self.norm_whole or self.values_are_keys or self.wide_gate or (self.extended and interleaved)
+                           or self.shaped)
         self.general = (self.hdv != self.hd or self.block is not None or self.head_gate or not self.own_kv
-                        or self.extended)
+                        or self.extended or self.shaped)
         self.wqkv = self.wo = self.q_norm = self.k_norm = None
 
     def weight_specs(self):
@@ -131,18 +154,29 @@ class Attention(Mixer):
             s.append(WeightSpec("rel", (self.distance_buckets[0], self.nh), "vector", ("normal", 0.5)))
         if self.learned_sink:
             s.append(WeightSpec("sink", (self.nh,), "vector", ("normal", 1.0)))
+        for n, rows in (("q", self.q_width), ("k", self.kv_width), ("v", self.v_width)):
+            if self.in_bias:
+                s.append(WeightSpec(f"{n}_proj.bias", (rows,), "vector", ("normal", 0.1)))
+            if self.conv > 0:
+                s.append(WeightSpec(f"{n}_conv.weight", (rows, self.conv), "vector", ("normal", 0.4)))
+        if self.value_mix is not None:
+            s.append(WeightSpec("vmix", (), "vector", ("normal", 0.5)))
         return s
 
     def cache_need(self):
         # kept first positions lie outside any ring of the window's size: the cache then holds all positions
-        return KVNeed(self.nkv, self.hd, None if self.keep_first else self.window, self.hdv if self.hdv != self.hd else None)
+        kv = KVNeed(self.nkv, self.hd, None if self.keep_first else self.window, self.hdv if self.hdv != self.hd else None)
+        if self.conv > 1:
+            return (kv, StateNeed((self.conv - 1, self.q_width + self.kv_width + self.v_width), "float32"))
+        return kv
 
     def kernel_needs(self, run_dtype):
         from ..kernels import attn_tc, catalog
+        shaping = [("rowwise.cu", ())] if self.shaped else []
         if run_dtype != torch.bfloat16:
-            return [("attn_simple.cu", ())]
+            return [("attn_simple.cu", ())] + shaping
         if self.general:
-            out = [("attn_simple.cu", ())]
+            out = [("attn_simple.cu", ())] + shaping
             if self.extended:
                 if self._fast_extended() and attn_tc.EXTENDED:
                     out.append(attn_tc.target(self.hd))
@@ -198,6 +232,10 @@ class Attention(Mixer):
                                  "position encoding must be a rotation of pairs")
             if self.general and self.position.rotation().interleaved and not self.place_rows:
                 raise ValueError("attention: the head-wise placement kernel rotates pairs (j, j + rotary_dim / 2) only")
+        names = ("q", "k", "v")
+        self.bias_qkv = torch.cat([tensors[f"{n}_proj.bias"].float() for n in names]).contiguous() if self.in_bias else None
+        self.conv_w = torch.cat([tensors[f"{n}_conv.weight"].float() for n in names], dim=0).contiguous() if self.conv > 0 else None
+        self.lam = tensors["vmix"].float().reshape(1).contiguous() if self.value_mix is not None else None
         self.sink_vals = tensors["sink"].float().contiguous() if self.learned_sink else None
         self.dist_bias = None
         if self.distance_buckets is not None:
@@ -238,6 +276,8 @@ class Attention(Mixer):
         if x is None:
             x = rt.arena.alloc((T, self.wqkv.shape[0]), torch.float32)
             rt.matmul(h, self.wqkv, x)
+        if self.shaped:
+            x = self._shape_projections(x, T, batch, cache, rt)
         q = rt.arena.alloc((T, self.q_width), rt.dtype)
         k_off = self.q_width if self.own_kv else None
         v_off = (k_off if self.values_are_keys else self.q_width + self.kv_width) if self.own_kv else None
@@ -273,6 +313,23 @@ class Attention(Mixer):
                             keep_first=self.keep_first, slopes=self.slopes, sink=self.sink, out_scale=self.out_scale,
                             softcap=self.softcap, dist_bias=self.dist_bias, sink_vals=self.sink_vals)
         rt.matmul(o, self.wo, residual, ops.EPI_ADD)
+
+    def _shape_projections(self, x, T, batch, cache, rt):
+        """Bias, the short convolution over time and the blending of values, in one kernel: the float32 sums of the
+        [q | k | v] product (whole or in K slices) become the rows that are normed, rotated and cached."""
+        C = self.q_width + self.kv_width + self.v_width
+        out = rt.arena.alloc((T, C), torch.float32)
+        mix = None
+        if self.value_mix is not None:
+            first = rt.carry(("value_mix", self.value_mix_key), T, self.v_width, torch.float32)
+            mix = (1 if self.value_mix == "source" else 2, self.q_width + self.kv_width, C, self.lam, first)
+        state = cache.states[0] if self.conv > 1 else None
+        rt.launches += 1
+        ops.causal_conv(x, self.conv_w, state, batch, out, bias=self.bias_qkv, mix=mix)
+        if self.conv > 1:
+            rt.launches += 1
+            ops.causal_conv_state(x, state, batch, bias=self.bias_qkv)
+        return out
 
     def forward(self, h, residual, batch, cache, rt, projected=None):
         if self.general:

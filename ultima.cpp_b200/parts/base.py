@@ -36,7 +36,7 @@ def part(kind: str, **params) -> PartSpec:
 
 
 FAMILIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "residual_gate", "entry",
-            "connection")
+            "connection", "input_filter", "tail")
 _TABLES: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
 
 
@@ -202,6 +202,28 @@ class Connection(Part):
     def write(self, xs, y, rt, then=None):
         """Put the sublayer's result y (float32 [T, width]) into the copies and clear y.  ``then`` = (connection, norm):
         also return what that next sublayer reads (one pass over the copies instead of two)."""
+        raise NotImplementedError
+
+
+class InputFilter(Part):
+    """What a sublayer's input passes between the norm and the sublayer: a map of the normed activations of the step's
+    tokens that may look back over a sequence's earlier tokens through per-sequence state (``cache_need``)."""
+    graph_safe = True
+
+    def cache_need(self):
+        return None
+
+    def forward(self, h, batch, cache, rt):
+        """h: activations [T, width] -> activations [T, width]; ``cache``: this part's share of the run's cache."""
+        raise NotImplementedError
+
+
+class Tail(Part):
+    """What a layer does to the residual stream behind its sublayers, with the step's tokens at hand."""
+    graph_safe = True
+
+    def forward(self, x, xa, batch, rt) -> None:
+        """Update x (float32 [T, width]) in place; xa: x in the activation type, as the join before left it."""
         raise NotImplementedError
 
 

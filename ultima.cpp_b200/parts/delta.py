@@ -1,5 +1,7 @@
-"""The gated delta-rule mixer: a recurrent layer with a matrix of state a head."""
+"""The delta-rule mixers: recurrent layers with a matrix of state a head."""
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -163,4 +165,93 @@ class GatedDelta(Mixer):
             ops.conv_state_update(p, conv_state, batch, self.channels, self.conv)
         ops.delta_scan(qn, kn, vc, beta, dec, o, S, batch, self.nh, self.nkv, self.hd, self.hdv)
         ops.delta_finish(o, gate_pre, self.o_norm, oa, self.nh, self.hdv, self.eps, silu_gate=self.gate_full)
+        rt.matmul(oa, self.wo, residual, ops.EPI_ADD)
+
+
+@register_part("mixer", "general_delta")
+class GeneralDelta(Mixer):
+    """The generalised delta rule: for each head a matrix S [D, D] in float32, zero at a sequence's start.  A token brings
+    r, k, v (``n_heads`` heads of size D each, plain projections), a decay for every head and key channel
+    w = exp(-exp(-1/2) * sigmoid(w_up(tanh(w_down h)) + w_bias)) and a removal rate for every head and key channel
+    a = sigmoid(a_proj h + a_bias).  With the unit key u = k / sqrt(sum k^2 + unit_eps) of each head:
+
+        S <- diag(w) S - (a * u) (u^T S) + k v^T        (both terms read the old S);      o = S^T r
+
+    Each head's o is divided by its root mean square (``eps``); the heads side by side are multiplied by a weight of all
+    heads' size and by sigmoid(gate_proj h), and go through the output projection into the stream the mixer is handed.
+
+    The projections that read the mixer's input are ONE product [r | k | v | gate | a | w_down] with float32 results (for
+    few tokens in K slices that the kernels add up); tanh(w_down h) in the activation type is the operand of the small
+    product w_up (padded to a multiple of 8 columns with zero weights).  Everything behind the products is float32."""
+
+    graph_safe = True
+    DECAY_SCALE = math.exp(-0.5)
+
+    def __init__(self, width: int, n_heads: int, head_dim: int, decay_rank: int, eps: float, unit_eps: float = 1e-6):
+        self.width, self.nh, self.hd, self.rank = int(width), int(n_heads), int(head_dim), int(decay_rank)
+        self.eps, self.unit_eps = float(eps), float(unit_eps)
+        self.inner = self.nh * self.hd
+        if self.hd > 256:
+            raise ValueError(f"general_delta: head size {self.hd} is more than the scan kernel holds (256)")
+        if self.rank < 1:
+            raise ValueError("general_delta: the decay's low-rank product needs an inner size of at least 1")
+        self.rank_pad = -(-self.rank // 8) * 8
+
+    def weight_specs(self):
+        W, V, n = WeightSpec, "vector", self.inner
+        return [W("r_proj.weight", (n, self.width)), W("k_proj.weight", (n, self.width)), W("v_proj.weight", (n, self.width)),
+                W("gate_proj.weight", (n, self.width)), W("a_proj.weight", (n, self.width)),
+                W("a_bias", (n,), V, ("normal", 0.5)),
+                W("w_down.weight", (self.rank, self.width)),
+                W("w_up.weight", (n, self.rank), "matrix", ("normal", 0.3)),
+                W("w_bias", (n,), V, ("normal", 0.5)),
+                W("o_norm.weight", (n,), V, ("one_plus_normal", 0.05)),
+                W("o_proj.weight", (self.width, n))]
+
+    def cache_need(self):
+        return StateNeed((self.nh, self.hd, self.hd), "float32")
+
+    def kernel_needs(self, run_dtype):
+        return [("delta.cu", ()), ("rowwise.cu", ())]
+
+    def bind(self, tensors, rt):
+        names = ["r_proj", "k_proj", "v_proj", "gate_proj", "a_proj", "w_down"]
+        ws = [tensors[n + ".weight"] for n in names]
+        if len({w.dtype for w in ws}) != 1:
+            raise ValueError("general_delta: the projections must share one element type")
+        self.w_in = torch.cat(ws, dim=0).contiguous()
+        n = self.inner
+        self.offs = (0, n, 2 * n, 4 * n)                 # r, k, v, removal rate
+        self.g_off, self.low_off = 3 * n, 5 * n
+        up = tensors["w_up.weight"]
+        if self.rank_pad != self.rank:
+            p = torch.zeros((n, self.rank_pad), dtype=up.dtype, device=up.device)
+            p[:, :self.rank] = up
+            up = p
+        self.w_up = up.contiguous()
+        self.a_bias = tensors["a_bias"].float().contiguous()
+        self.w_bias = tensors["w_bias"].float().contiguous()
+        self.o_norm = tensors["o_norm.weight"].float().contiguous()
+        self.wo = tensors["o_proj.weight"].contiguous()
+
+    def forward(self, h, residual, batch, cache, rt):
+        T, n = h.shape[0], self.inner
+        S = cache.states[0]
+        f32 = torch.float32
+        p = rt.matmul_parts(h, self.w_in)
+        if p is None:
+            p = rt.arena.alloc((T, self.w_in.shape[0]), f32)
+            rt.matmul(h, self.w_in, p)
+        low = rt.arena.alloc((T, self.rank_pad), rt.dtype)
+        rt.launches += 1
+        ops.take_cols(p, self.low_off, self.rank, low, tanh=True)
+        wpre = rt.arena.alloc((T, n), f32)
+        rt.matmul(low, self.w_up, wpre)
+        rn, un, kraw, rem, dec, vc, o = (rt.arena.alloc((T, n), f32) for _ in range(7))
+        oa = rt.arena.alloc((T, n), rt.dtype)
+        rt.launches += 3
+        ops.gdelta_prepare(p, self.offs, self.a_bias, wpre, self.w_bias, rn, un, kraw, rem, dec, vc, self.nh, self.hd,
+                           self.unit_eps, self.DECAY_SCALE)
+        ops.delta_scan(rn, un, vc, None, dec, o, S, batch, self.nh, self.nh, self.hd, self.hd, rem=rem, kraw=kraw)
+        ops.delta_finish(o, p[..., self.g_off:self.g_off + n], self.o_norm, oa, self.nh, self.hd, self.eps)
         rt.matmul(oa, self.wo, residual, ops.EPI_ADD)

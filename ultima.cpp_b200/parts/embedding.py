@@ -14,21 +14,39 @@ class TokenTable(Part):
     outside the vocabulary is refused on the host before the launch; the kernel checks again
     and raises a flag."""
 
-    def __init__(self, vocab_size: int, width: int):
+    def __init__(self, vocab_size: int, width: int, norm: str | None = None, eps: float = 0.0):
+        """``norm``: "layer" or "rms": the gathered rows pass a norm with a weight of its own (tensor ``norm.weight``) and
+        ``eps`` before they enter the stream (float32 in and out)."""
         self.vocab_size, self.width = int(vocab_size), int(width)
-        self.table = None
+        if norm not in (None, "layer", "rms"):
+            raise ValueError("token_table: norm is 'layer', 'rms' or None")
+        self.norm, self.eps = norm, float(eps)
+        self.table = self.norm_w = None
 
     def weight_specs(self):
-        return [WeightSpec("weight", (self.vocab_size, self.width))]
+        s = [WeightSpec("weight", (self.vocab_size, self.width))]
+        if self.norm:
+            s.append(WeightSpec("norm.weight", (self.width,), "vector", ("one_plus_normal", 0.05)))
+        return s
+
+    def kernel_needs(self, run_dtype):
+        return [("rowwise.cu", ())] if self.norm == "layer" else []
 
     def bind(self, tensors, rt):
         self.table = tensors["weight"].contiguous()
         self.status = rt.status[0:1]
+        if self.norm:
+            self.norm_w = tensors["norm.weight"].float().contiguous()
 
     def forward(self, ids, rt):
         x = rt.arena.alloc((ids.numel(), self.width), torch.float32)
         rt.launches += 1
         ops.embed(self.table, ids, x, self.status)
+        if self.norm:
+            out = rt.arena.alloc((ids.numel(), self.width), torch.float32)
+            rt.launches += 1
+            (ops.layernorm if self.norm == "layer" else ops.rmsnorm)(x, self.norm_w, out, self.eps)
+            return out
         return x
 
 

@@ -109,3 +109,40 @@ class GatedReLU(GatedClamped):
 
     def __init__(self, width: int, inner: int):
         super().__init__(width, inner, limit=float("inf"), alpha=float("inf"), shift=0.0)
+
+
+_ACTIVATIONS = {"gelu_erf": ops.UNARY_GELU_ERF, "relu_squared": ops.UNARY_RELU_SQUARED}
+
+
+@register_part("feed_forward", "plain_mlp")
+class PlainMLP(FeedForward):
+    """down(act(up(h))), no gate and no biases, added to the stream it is handed; ``activation`` is "gelu_erf" (the exact
+    GELU, 0.5 z (1 + erf(z / sqrt 2))) or "relu_squared" (max(z, 0)^2).  The activation is float32 arithmetic on the up
+    product's float32 sums, rounded once to the activation type."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, activation: str):
+        self.width, self.inner, self.activation = int(width), int(inner), str(activation)
+        if self.activation not in _ACTIVATIONS:
+            raise ValueError(f"plain_mlp: activation must be one of {', '.join(_ACTIVATIONS)}, got {activation!r}")
+
+    def weight_specs(self):
+        return [WeightSpec("up_proj.weight", (self.inner, self.width)),
+                WeightSpec("down_proj.weight", (self.width, self.inner))]
+
+    def kernel_needs(self, run_dtype):
+        return [("rowwise.cu", ())]
+
+    def bind(self, tensors, rt):
+        self.wu = tensors["up_proj.weight"].contiguous()
+        self.wd = tensors["down_proj.weight"].contiguous()
+
+    def forward(self, h, residual, batch, rt):
+        T = h.shape[0]
+        u = rt.arena.alloc((T, self.inner), torch.float32)
+        rt.matmul(h, self.wu, u)
+        a = rt.arena.alloc((T, self.inner), rt.dtype)
+        rt.launches += 1
+        ops.unary(u, a, _ACTIVATIONS[self.activation])
+        rt.matmul(a, self.wd, residual, ops.EPI_ADD)

@@ -34,3 +34,31 @@ class RMSNorm(Norm):
         [T, width].  ``h`` receives the new x in h's type (the next sublayer's input); ``clear`` zeroes y."""
         rt.launches += 1
         ops.rmsnorm_add(y, self.weight, x, self.eps, h=h, clear_y=clear)
+
+
+@register_part("norm", "layer")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w, the variance being the mean of the squared deviations; a weight and no
+    bias.  ``scale``: a constant folded into the weight (a model that multiplies its logits by a constant puts it on
+    the final norm).  Input is the float32 residual stream, sums are float32, the output has the activation type."""
+
+    def __init__(self, width: int, eps: float, scale: float = 1.0):
+        self.width, self.eps, self.scale = int(width), float(eps), float(scale)
+        self.weight = None
+
+    def weight_specs(self):
+        return [WeightSpec("weight", (self.width,), "vector", ("one_plus_normal", 0.05))]
+
+    def kernel_needs(self, run_dtype):
+        return [("rowwise.cu", ())]
+
+    def bind(self, tensors, rt):
+        w = tensors["weight"].float()
+        self.weight = (w * self.scale if self.scale != 1.0 else w).contiguous()
+
+    def forward(self, x, rt, rows=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = rt.arena.alloc((n, self.width), rt.dtype)
+        rt.launches += 1
+        ops.layernorm(x, self.weight, out, self.eps, rows)
+        return out

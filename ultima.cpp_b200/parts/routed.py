@@ -34,6 +34,13 @@ class RoutedExperts(FeedForward):
     renormalised.  The last ``n_identity`` outputs are identity experts: they hand the input on, scaled by the choice's weight, and
     have no tensors.  ``shared_inner``: one more gated feed-forward that every token uses, added unweighted.
 
+    Other routers and experts of the same family, each a parameter:
+      score="sigmoid"        s = sigmoid(z), every output on its own, instead of the softmax
+      group_score="top2_sum" a group's score is the sum of its two largest choice scores instead of the largest
+      normalise=True         the chosen outputs' weights are divided by their sum (+ 1e-20)
+      weight_scale           a constant on the weights (behind the normalisation)
+      expert="relu_squared"  an expert (and the shared one) is down(max(up h, 0)^2): no gate matrix
+
     On the GPU: the router's product with float32 sums (CUDA cores and float32 weights; in a bfloat16 run the stored
     bfloat16 weights on the tensor cores, whose products of two bfloat16 numbers are exact); one kernel picks and counts, one lays
     out the experts' segments and tiles, one hands every (token, choice) its sorted row; the experts' gate/up and
@@ -47,7 +54,8 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, width: int, inner: int, n_experts: int, top: int, n_identity: int = 0, groups: tuple | None = None,
-                 shared_inner: int | None = None, correction: bool = True):
+                 shared_inner: int | None = None, correction: bool = True, score: str = "softmax", group_score: str = "max",
+                 normalise: bool = False, weight_scale: float = 1.0, expert: str = "gated_silu"):
         self.width, self.inner, self.ne, self.top = int(width), int(inner), int(n_experts), int(top)
         self.ni = int(n_identity or 0)
         self.n_out = self.ne + self.ni
@@ -57,8 +65,17 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed_experts: top must not exceed the router's outputs, which divide into equal groups")
         if self.n_out > 1024 or self.ne < 1:
             raise ValueError("routed_experts: the router kernel takes up to 1,024 outputs, at least one of them an expert")
-        self.shared = build_part("feed_forward", part("gated_silu", width=self.width, inner=int(shared_inner))) \
-            if shared_inner else None
+        if score not in ("softmax", "sigmoid") or group_score not in ("max", "top2_sum") or expert not in ("gated_silu", "relu_squared"):
+            raise ValueError("routed_experts: score is 'softmax' or 'sigmoid', group_score 'max' or 'top2_sum', expert "
+                             "'gated_silu' or 'relu_squared'")
+        self.mode = ((ops.ROUTE_SIGMOID if score == "sigmoid" else 0) | (ops.ROUTE_GROUP_TOP2 if group_score == "top2_sum" else 0)
+                     | (ops.ROUTE_NORMALISE if normalise else 0))
+        self.weight_scale, self.gated = float(weight_scale), expert == "gated_silu"
+        if not self.gated and self.ni:
+            raise ValueError("routed_experts: identity experts go with gated experts")
+        shared = part("gated_silu", width=self.width, inner=int(shared_inner or 0)) if self.gated else \
+            part("plain_mlp", width=self.width, inner=int(shared_inner or 0), activation="relu_squared")
+        self.shared = build_part("feed_forward", shared) if shared_inner else None
 
     def weight_specs(self):
         W = WeightSpec
@@ -66,8 +83,9 @@ class RoutedExperts(FeedForward):
         if self.correction:
             s.append(W("correction", (self.n_out,), "vector", ("normal", 0.05)))
         for e in range(self.ne):
-            s += [W(f"experts.{e}.gate_proj.weight", (self.inner, self.width)),
-                  W(f"experts.{e}.up_proj.weight", (self.inner, self.width)),
+            if self.gated:
+                s.append(W(f"experts.{e}.gate_proj.weight", (self.inner, self.width)))
+            s += [W(f"experts.{e}.up_proj.weight", (self.inner, self.width)),
                   W(f"experts.{e}.down_proj.weight", (self.width, self.inner))]
         if self.shared is not None:
             s += [W("shared." + w.name, w.shape, w.kind, w.init) for w in self.shared.weight_specs()]
@@ -75,6 +93,8 @@ class RoutedExperts(FeedForward):
 
     def kernel_needs(self, run_dtype):
         out = [("routed.cu", ())]
+        if not self.gated:
+            out.append(("rowwise.cu", ()))
         if run_dtype == torch.bfloat16:
             out.append(("gemm_tcgen05.cu", ()))
         return out
@@ -87,12 +107,14 @@ class RoutedExperts(FeedForward):
         self.w_router = wr.contiguous() if (wr.dtype == torch.bfloat16 and rt.dtype == torch.bfloat16 and self.width % 8 == 0) \
             else wr.float().contiguous()
         self.corr = tensors["correction"].float().contiguous() if self.correction else None
-        g0 = tensors["experts.0.gate_proj.weight"]
-        self.w_gu = torch.empty((self.ne, 2 * self.inner, self.width), dtype=g0.dtype, device=g0.device)
+        g0 = tensors["experts.0.up_proj.weight"]
+        rows = 2 * self.inner if self.gated else self.inner          # [gate ; up] or up alone
+        self.w_gu = torch.empty((self.ne, rows, self.width), dtype=g0.dtype, device=g0.device)
         self.w_down = torch.empty((self.ne, self.width, self.inner), dtype=g0.dtype, device=g0.device)
         for e in range(self.ne):
-            self.w_gu[e, :self.inner] = tensors[f"experts.{e}.gate_proj.weight"]
-            self.w_gu[e, self.inner:] = tensors[f"experts.{e}.up_proj.weight"]
+            if self.gated:
+                self.w_gu[e, :self.inner] = tensors[f"experts.{e}.gate_proj.weight"]
+            self.w_gu[e, rows - self.inner:] = tensors[f"experts.{e}.up_proj.weight"]
             self.w_down[e] = tensors[f"experts.{e}.down_proj.weight"]
         if self.shared is not None:
             self.shared.bind({w.name: tensors["shared." + w.name] for w in self.shared.weight_specs()}, rt)
@@ -115,9 +137,13 @@ class RoutedExperts(FeedForward):
         src_rows = rt.arena.alloc((T * top,), i32)
         act = rt.arena.alloc((T * top, self.inner), rt.dtype)
         y = rt.arena.alloc((T * top, self.width), f32)
-        w_gate, w_up = self.w_gu[:, :self.inner], self.w_gu[:, self.inner:]
+        if self.gated:
+            w_gate, w_up = self.w_gu[:, :self.inner], self.w_gu[:, self.inner:]
+            first = (w_gate, act, ops.EPI_SWIGLU, w_up)
+        else:
+            first = (self.w_gu, rt.arena.alloc((T * top, self.inner), f32), ops.EPI_STORE, None)     # the up product's sums
         # the tensor-core products take both or neither: their tiles are cut to the rows an expert gets on average
-        fast = (rt.grouped_on_tensor_cores(h, w_gate, act, ops.EPI_SWIGLU, w_up)
+        fast = (rt.grouped_on_tensor_cores(h, first[0], first[1], first[2], first[3])
                 and rt.grouped_on_tensor_cores(act, self.w_down, y))
         tile = ops.ROUTE_TILE
         if fast:
@@ -128,10 +154,11 @@ class RoutedExperts(FeedForward):
         counts, cursor, seg_start, n_tiles = self.ws[:ne], self.ws[ne:2 * ne], self.ws[2 * ne:3 * ne], self.ws[3 * ne:3 * ne + 1]
         if T <= ops.ROUTE_SMALL_TOKENS and self._small_fits:
             rt.launches += 1                  # few tokens: the three steps as one launch of one block
-            ops.route_small(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, tiles, n_tiles, row_pos, src_rows, tile)
+            ops.route_small(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, tiles, n_tiles, row_pos, src_rows, tile,
+                            mode=self.mode, wscale=self.weight_scale)
         else:
             rt.launches += 3
-            ops.route(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, counts)
+            ops.route(z, self.corr, ne, top, self.groups[0], self.groups[1], idx, wts, counts, mode=self.mode, wscale=self.weight_scale)
             ops.route_plan(counts, cursor, seg_start, tiles, n_tiles, ne, tile)
             ops.route_scatter(idx, seg_start, cursor, row_pos, src_rows, ne)
         plan = RoutePlan(tiles, n_tiles, src_rows, max_tiles, T * top, tile=tile)
@@ -140,9 +167,12 @@ class RoutedExperts(FeedForward):
             rt.launches += 1
             ops.route_gather(h, row_pos, rows)
             plan.gather = False
-            rt.matmul_grouped(rows, w_gate, act, plan, ops.EPI_SWIGLU, w2=w_up)
+            rt.matmul_grouped(rows, first[0], first[1], plan, first[2], w2=first[3])
         else:
-            rt.matmul_grouped(h, w_gate, act, plan, ops.EPI_SWIGLU, w2=w_up)
+            rt.matmul_grouped(h, first[0], first[1], plan, first[2], w2=first[3])
+        if not self.gated:
+            rt.launches += 1
+            ops.unary(first[1], act, ops.UNARY_RELU_SQUARED)
         plan.gather = False
         rt.matmul_grouped(act, self.w_down, y, plan)
         rt.launches += 1

@@ -106,3 +106,95 @@ class StateSpaceDual(Mixer):
         ops.ssm_scan(xbc, dtv, dec, self.d_skip, y, S, batch, self.nh, self.hd, self.n_state, self.ng)
         ops.ssm_finish(y, p, self.shape, self.o_norm, ya, self.norm_groups, self.eps, self.out_scale)
         rt.matmul(ya, self.wo, residual, ops.EPI_ADD)
+
+
+@register_part("mixer", "selective_scan")
+class SelectiveScan(Mixer):
+    """The selective scan with a decay for every (channel, state element) (the first Mamba form).  ``in_proj`` gives a row
+    [x | z] of ``inner`` columns each; x passes a causal convolution of ``conv`` taps over time (one filter a channel with a
+    bias, the last tap on the current token, zeros before the sequence) and SiLU; ``x_proj`` of that gives
+    [dt | B | C] (``dt_rank``, ``state``, ``state`` columns); dt = softplus(dt_proj(dt) + dt_bias), one a channel;
+    A = -exp(a_log) [inner, state].  For channel c and state element n, in float32, zero at a sequence's start:
+
+        S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;     y_c = sum_n S[c, n] C_n + d_skip[c] x_c
+
+    y silu(z) goes through the output projection into the stream the mixer is handed.  The convolution's last
+    ``conv - 1`` inputs are state too.  Step sizes, softplus, exponentials and S are float32; the products' operands
+    have the activation type (for few tokens the input product runs in K slices that the kernels add up)."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, state: int, dt_rank: int, conv: int):
+        self.width, self.inner, self.n_state = int(width), int(inner), int(state)
+        self.dt_rank, self.conv = int(dt_rank), int(conv)
+        if not (1 <= self.conv <= 16):
+            raise ValueError(f"selective_scan: a convolution of {self.conv} taps is not one the kernels take (1 to 16)")
+        if not (1 <= self.n_state <= 256):
+            raise ValueError(f"selective_scan: a state of {self.n_state} elements is more than the scan kernel holds (256)")
+        if self.dt_rank < 1:
+            raise ValueError("selective_scan: dt_rank must be at least 1")
+        self.rank_pad = -(-self.dt_rank // 8) * 8
+
+    def weight_specs(self):
+        W, V = WeightSpec, "vector"
+        return [W("in_proj.weight", (2 * self.inner, self.width)),
+                W("conv.weight", (self.inner, self.conv), V, ("normal", 0.3)),
+                W("conv.bias", (self.inner,), V, ("normal", 0.1)),
+                W("x_proj.weight", (self.dt_rank + 2 * self.n_state, self.inner)),
+                W("dt_proj.weight", (self.inner, self.dt_rank), "matrix", ("normal", 0.1)),
+                W("dt_bias", (self.inner,), V, ("normal", 0.5)),
+                W("a_log", (self.inner, self.n_state), V, ("normal", 0.5)),
+                W("d_skip", (self.inner,), V, ("one_plus_normal", 0.2)),
+                W("o_proj.weight", (self.width, self.inner))]
+
+    def cache_need(self):
+        S = StateNeed((self.inner, self.n_state), "float32")
+        return (S, StateNeed((self.conv - 1, self.inner), "float32")) if self.conv > 1 else S
+
+    def kernel_needs(self, run_dtype):
+        return [("ssm.cu", ()), ("rowwise.cu", ())]
+
+    def bind(self, tensors, rt):
+        self.w_in = tensors["in_proj.weight"].contiguous()
+        self.w_x = tensors["x_proj.weight"].contiguous()
+        wd = tensors["dt_proj.weight"]
+        if self.rank_pad != self.dt_rank:                 # an aligned operand: columns of zeros
+            p = torch.zeros((self.inner, self.rank_pad), dtype=wd.dtype, device=wd.device)
+            p[:, :self.dt_rank] = wd
+            wd = p
+        self.w_dt = wd.contiguous()
+        self.wo = tensors["o_proj.weight"].contiguous()
+        self.conv_w = tensors["conv.weight"].float().contiguous()
+        self.conv_b = tensors["conv.bias"].float().contiguous()
+        self.dt_bias = tensors["dt_bias"].float().contiguous()
+        self.A = (-torch.exp(tensors["a_log"].float())).contiguous()
+        self.d_skip = tensors["d_skip"].float().contiguous()
+
+    def forward(self, h, residual, batch, cache, rt):
+        T = h.shape[0]
+        f32 = torch.float32
+        S = cache.states[0]
+        conv_state = cache.states[1] if self.conv > 1 else None
+        p = rt.matmul_parts(h, self.w_in)               # few tokens: K in slices, summed by the kernels that read them
+        if p is None:
+            p = rt.arena.alloc((T, 2 * self.inner), f32)
+            rt.matmul(h, self.w_in, p)
+        xc = rt.arena.alloc((T, self.inner), rt.dtype)
+        rt.launches += 1
+        ops.causal_conv(p, self.conv_w, conv_state, batch, xc, silu=True, out_bias=self.conv_b)
+        if self.conv > 1:
+            rt.launches += 1
+            ops.causal_conv_state(p, conv_state, batch)
+        bc = rt.arena.alloc((T, self.dt_rank + 2 * self.n_state), f32)
+        rt.matmul(xc, self.w_x, bc)
+        low = rt.arena.alloc((T, self.rank_pad), rt.dtype)
+        rt.launches += 1
+        ops.take_cols(bc, 0, self.dt_rank, low)
+        dtp = rt.arena.alloc((T, self.inner), f32)
+        rt.matmul(low, self.w_dt, dtp)
+        y = rt.arena.alloc((T, self.inner), rt.dtype)
+        rt.launches += 1
+        z = p[..., self.inner:]
+        ops.mamba1_scan(xc, dtp, self.dt_bias, bc, self.dt_rank, self.dt_rank + self.n_state, self.A, self.d_skip, z, y, S,
+                        batch, self.n_state)
+        rt.matmul(y, self.wo, residual, ops.EPI_ADD)
