@@ -237,3 +237,36 @@ def forward(cfg, W, tokens, dt=torch.float64, taps=None):
             taps.append(x.clone())
     x = layer_norm(x, W["final.norm"], eps)
     return x @ W["embed"].T * cfg.get("logit_scale", 1.0)
+
+
+def read_folder(model_dir: str):
+    """(config.json's dictionary, stored name -> float64 tensor) read with nothing but the file format."""
+    import json
+    import os
+    import struct
+
+    import numpy as np
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    with open(os.path.join(model_dir, "model.safetensors"), "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        data = f.read()
+    header.pop("__metadata__", None)
+    W = {}
+    for name, e in header.items():
+        raw = data[e["data_offsets"][0]:e["data_offsets"][1]]
+        if e["dtype"] == "BF16":
+            a = (np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16).view(np.float32)
+        elif e["dtype"] == "F32":
+            a = np.frombuffer(raw, dtype="<f4")
+        else:
+            raise ValueError(f"plain reader: dtype {e['dtype']} of {name}")
+        W[name] = torch.from_numpy(a.astype(np.float64).reshape(e["shape"]))
+    return cfg, W
+
+
+def logits(cfg, W, tokens):
+    """float64 numpy [T, vocab]."""
+    with torch.no_grad():
+        return forward(cfg, W, tokens, torch.float64).numpy()

@@ -96,7 +96,7 @@ def counter_fill(shape, key: int, shift: float, std: float, chunk: int = 1 << 16
     for a in range(0, n, chunk):
         b = min(n, a + chunk)
         out[a:b] = sh + sd * counter_normal(key, a, b - a)
-    return torch.from_numpy(out).view(*shape)
+    return torch.from_numpy(out).reshape(tuple(int(d) for d in shape))
 
 
 def _tensor_seed(seed: int, name: str) -> int:
