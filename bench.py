@@ -509,6 +509,30 @@ def vusalix_config(z):
             "layers": layers}
 
 
+def bizepel_config(z):
+    """Layers in fours: attention (short convolutions, window with kept first positions, values blended with the first
+    such layer's), the generalised delta rule, attention again, the selective scan; the first layer with a dense
+    feed-forward, the others routed with an active size (top experts and the shared one) of the dense models' ff; every
+    sublayer behind an input convolution and a layer scale; a per-layer token input."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "conv": 4, "rot": {"base": 10000.0, "dims": z["dim"] // 2}, "mask": {"size": 1024, "keep_first": 4}, "v_mix": True}
+    delta = {"heads": z["width"] // 64, "dim": 64, "decay_rank": 64}
+    scan = {"inner": 2 * z["width"], "state": 16, "dt_rank": z["width"] // 16, "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 6}, "shared": {"ff": z["ff"] // 3},
+           "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    kinds = ("attention", "general_delta", "attention", "mamba1")
+    mixers = {"attention": att, "general_delta": delta, "mamba1": scan}
+    layers = [{"type": kinds[i % 4], "mixer": dict(mixers[kinds[i % 4]]),
+               "mlp": {"kind": "dense", "ff": z["ff"]} if i == 0 else dict(moe)} for i in range(z["layers"])]
+    return {"architecture": "Bizepel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "token_side": {"dim": 256}, "logit_scale": 1.0, "layers": layers}
+
+
+def bizepel_times(args):
+    return design_times(args, "bizepel", (("bizepel", bizepel_config), ("vusalix", vusalix_config), ("tinuzen", tinuzen_config),
+                                          ("qwen3", qwen3_config_like)))
+
+
 def vusalix_times(args):
     return design_times(args, "vusalix", (("vusalix", vusalix_config), ("sugizen", sugizen_config), ("qwen3", qwen3_config_like)))
 
@@ -953,7 +977,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks", "sugizen", "tinuzen", "vusalix"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks", "sugizen", "tinuzen", "vusalix",
+                             "bizepel"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
                          "timeline: every kernel of a decode step with its begin and end inside the graph "
                          "(timeline-prefill: of a prompt); "
@@ -962,7 +987,8 @@ def main():
                          "sugizen: prompt and decode throughput of the Sugizen design beside Qwen3 at equal layer sizes "
                          "(two widths, eight layers), with every kernel's time in a prompt and in a decode step; "
                          "tinuzen: the same for the Tinuzen design beside Sugizen and Qwen3; "
-                         "vusalix: the same for the Vusalix design beside Sugizen and Qwen3")
+                         "vusalix: the same for the Vusalix design beside Sugizen and Qwen3; "
+                         "bizepel: the same for the Bizepel design beside Vusalix, Tinuzen and Qwen3")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
@@ -999,6 +1025,8 @@ def main():
         return tinuzen_times(args)
     if args.only == "vusalix":
         return vusalix_times(args)
+    if args.only == "bizepel":
+        return bizepel_times(args)
     if args.config != "8b":
         return run_other(args)
     return run_ours(args)

@@ -50,7 +50,16 @@ struct GemmParams {
     // u' = clamp(u, -limit, limit); +inf, 1 and 0 give silu(g) * u with the same bits as without them; alpha = +inf
     // is the hard limit max(g', 0) * (u' + shift)
     float act_limit, act_alpha, act_shift;
+    // EPI_STORE: what is stored is a function of the sum: 0 the sum itself, 1 the exact GELU 0.5 v (1 + erf(v / sqrt 2)),
+    // 2 the squared rectifier max(v, 0)^2 (whole K only: a slice's partial sum has no activation)
+    int unary;
 };
+
+__device__ __forceinline__ float unary_of(int kind, float v) {
+    if (kind == 1) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+    if (kind == 2) { const float r = fmaxf(v, 0.f); return r * r; }
+    return v;
+}
 
 __device__ __forceinline__ float gate_product(const GemmParams& p, float g, float u) {
     g = fminf(g, p.act_limit);
@@ -63,6 +72,7 @@ static void set_gate_constants(GemmParams& p, const float* gate) {
     p.act_limit = gate ? gate[0] : INFINITY;
     p.act_alpha = gate ? gate[1] : 1.0f;
     p.act_shift = gate ? gate[2] : 0.0f;
+    p.unary = gate ? (int)gate[3] : 0;                 // (the constants come as four floats)
 }
 
 template <int BN, int EPI, int KB = 0>
@@ -125,7 +135,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                 if (t >= p.T) break;
                 const float v = __uint_as_float(r[c]);
                 TO* dst = out + (long long)t * p.ldo + n;
-                if (EPI == EPI_STORE) *dst = from_f32<TO>(v);
+                if (EPI == EPI_STORE) *dst = from_f32<TO>(unary_of(p.unary, v));
                 else if (EPI == EPI_ADD) {
                     // a reduction at the memory side: no load, no wait; one writer an element
                     // unless K is split, so the sum's order is fixed in that case
@@ -930,7 +940,7 @@ static int launch_grouped_bn(const CUtensorMap* mw, const CUtensorMap* mw2, cons
 UB_API int ub_gemm_tc_grouped(const void* map_w, const void* map_w2, const void* map_a, void* out, int o_dtype, long long ldo,
                               int T, int N, int K, int bn, int epi, const void* tiles, const int* n_tiles, int max_tiles,
                               int n_mats, long long w_row_step, int a_col_step, long long o_col_step, int* error,
-                              cudaStream_t st) {
+                              const float* gate, cudaStream_t st) {
     if (N <= 0 || (tiles ? max_tiles <= 0 : (T <= 0 || n_mats <= 0))) return 0;
     if (K <= 0 || (tiles && !n_tiles) || (a_col_step % 8) != 0) return UB_ERR_ARG;
     if (epi == EPI_SWIGLU && !map_w2) return UB_ERR_ARG;
@@ -939,7 +949,7 @@ UB_API int ub_gemm_tc_grouped(const void* map_w, const void* map_w2, const void*
     p.T = T; p.N = N; p.K = K;
     p.kb_per_split = (K + BK - 1) / BK;
     p.atomic = 0; p.share_tail = 0; p.error = error;
-    set_gate_constants(p, nullptr);
+    set_gate_constants(p, gate);
     GroupParams gp;
     gp.tiles = (const int4*)tiles; gp.n_tiles = n_tiles; gp.w_row_step = w_row_step; gp.a_col_step = a_col_step;
     gp.o_col_step = o_col_step;

@@ -8,7 +8,8 @@
 //                    slices, plus an optional bias), the inputs of before the step read from per-sequence state,
 //                    zeros before a sequence's start; optionally u_t + y_t, a bias of its own, SiLU; optionally a column
 //                    range blended with another layer's values of the same token (or handed out for that)
-//   causal_conv_state   the last taps - 1 inputs of (state ++ step) become the state
+//   causal_conv_state   the last taps - 1 inputs of (state ++ step) become the state (in a step of one token a sequence a
+//                    channel's state has one reader, the thread that convolves it, which then moves it on itself)
 //   take_cols        a column range of a projection row (summed over its K slices), optionally through tanh,
 //                    into the activation type, padded with zeros to an aligned width
 //   unary            the exact (erf) GELU or the square of the rectifier, element by element
@@ -122,7 +123,7 @@ __device__ __forceinline__ float conv_input(const ConvIn& in, long long t, int c
 // layer blends them into its own); 2: they become (1 - lam) * own + lam * shared[t].
 template <typename TX, typename TO>
 __global__ void __launch_bounds__(256)
-causal_conv_kernel(ConvIn in, const float* __restrict__ w, const float* __restrict__ state, const int* __restrict__ tok_seq,
+causal_conv_kernel(ConvIn in, const float* __restrict__ w, float* __restrict__ state, int update_state, const int* __restrict__ tok_seq,
                    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, TO* __restrict__ out, long long ldo,
                    int n_tokens, int C, int taps, int add_input, int act, int mix_mode, int mix_lo, int mix_hi,
                    const float* __restrict__ lam, float* __restrict__ shared, const float* __restrict__ out_bias) {
@@ -137,12 +138,14 @@ causal_conv_kernel(ConvIn in, const float* __restrict__ w, const float* __restri
         const int seq = tok_seq[t];
         const int r = (int)t - seq_start[seq];
         const int K = taps - 1;
-        const float* st = state + (long long)seq_slot[seq] * K * C;
+        float* st = state + (long long)seq_slot[seq] * K * C;
         acc = 0.f;
         for (int j = K; j >= 1; --j) {                 // oldest input first
             const float xv = (r - j >= 0) ? conv_input<TX>(in, t - j, c) : st[(long long)(K + r - j) * C + c];
             acc = fmaf(w[(long long)c * taps + (K - j)], xv, acc);
+            if (update_state && j < K) st[(long long)(K - 1 - j) * C + c] = xv;      // r = 0: the input j back becomes j + 1 back
         }
+        if (update_state && K > 0) st[(long long)(K - 1) * C + c] = u;
         acc = fmaf(w[(long long)c * taps + K], u, acc);
         if (add_input) acc += u;
     }
@@ -154,6 +157,66 @@ causal_conv_kernel(ConvIn in, const float* __restrict__ w, const float* __restri
         else { const float l = *lam; acc = (1.0f - l) * acc + l * *sh; }
     }
     out[t * ldo + c] = from_f32<TO>(acc);
+}
+
+// The same for 2 to 4 taps with a thread walking CONV_TILE tokens of its channel in a row: an input is read once and kept
+// for the tokens behind it.  The first K tokens of a tile, and a sequence's first K tokens of the step, take their
+// earlier inputs the long way (rows of the step, or the state).
+constexpr int CONV_TILE = 16;
+
+template <typename TX, typename TO, int K>
+__global__ void __launch_bounds__(256)
+causal_conv_tile_kernel(ConvIn in, const float* __restrict__ w, float* __restrict__ state, int update_state,
+                        const int* __restrict__ tok_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                        TO* __restrict__ out, long long ldo, int n_tokens, int C, int add_input, int act, int mix_mode, int mix_lo,
+                        int mix_hi, const float* __restrict__ lam, float* __restrict__ shared, const float* __restrict__ out_bias) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float wt[K + 1], win[K];                           // win[j - 1]: the input j tokens back
+#pragma unroll
+    for (int j = 0; j <= K; ++j) wt[j] = w[(long long)c * (K + 1) + j];
+#pragma unroll
+    for (int j = 0; j < K; ++j) win[j] = 0.f;
+    const float ob = out_bias ? out_bias[c] : 0.f;
+    const bool mixes = mix_mode && c >= mix_lo && c < mix_hi;
+    const float l = (mixes && mix_mode == 2) ? *lam : 0.f;
+    const long long tbase = (long long)blockIdx.x * CONV_TILE;
+    for (int i = 0; i < CONV_TILE; ++i) {
+        const long long t = tbase + i;
+        if (t >= n_tokens) break;
+        const float u = conv_input<TX>(in, t, c);
+        const int seq = tok_seq[t];
+        const int r = (int)t - seq_start[seq];
+        float acc = 0.f;
+        if (i >= K && r >= K) {
+#pragma unroll
+            for (int j = K; j >= 1; --j) acc = fmaf(wt[K - j], win[j - 1], acc);
+        } else {
+            float* st = state + (long long)seq_slot[seq] * K * C;
+#pragma unroll
+            for (int j = K; j >= 1; --j) {
+                const float xv = (r - j >= 0) ? conv_input<TX>(in, t - j, c) : st[(long long)(K + r - j) * C + c];
+                acc = fmaf(wt[K - j], xv, acc);
+                if (update_state && j < K) st[(long long)(K - 1 - j) * C + c] = xv;
+            }
+            if (update_state) st[(long long)(K - 1) * C + c] = u;
+        }
+        acc = fmaf(wt[K], u, acc);
+        if (add_input) acc += u;
+        acc += ob;
+        if (act == 1) acc *= rw_sigmoid(acc);
+        if (mixes) {
+            float* sh = shared + t * (mix_hi - mix_lo) + (c - mix_lo);
+            if (mix_mode == 1) *sh = acc;
+            else acc = (1.0f - l) * acc + l * *sh;
+        }
+        out[t * ldo + c] = from_f32<TO>(acc);
+#pragma unroll
+        for (int j = K - 1; j >= 1; --j) win[j] = win[j - 1];
+        win[0] = u;
+    }
 }
 
 // One thread a (sequence, channel).
@@ -177,7 +240,7 @@ __global__ void causal_conv_state_kernel(ConvIn in, float* __restrict__ state, c
 }
 
 UB_API int ub_causal_conv(const void* x, int x_dtype, long long ldx, int n_parts, long long part_stride, int col_off,
-                          const float* bias, const float* w, const float* state, const int* tok_seq, const int* seq_start,
+                          const float* bias, const float* w, float* state, int update_state, const int* tok_seq, const int* seq_start,
                           const int* seq_slot, void* out, int out_dtype, long long ldo, int n_tokens, int C, int taps,
                           int add_input, int act, int mix_mode, int mix_lo, int mix_hi, const float* lam, float* shared,
                           const float* out_bias, cudaStream_t st) {
@@ -185,16 +248,28 @@ UB_API int ub_causal_conv(const void* x, int x_dtype, long long ldx, int n_parts
     if (taps < 0 || taps > RW_MAX_TAPS || n_parts < 1 || (taps > 1 && !state) || (taps > 0 && !w)) return UB_ERR_ARG;
     if (mix_mode && (!shared || mix_lo < 0 || mix_hi > C || mix_lo >= mix_hi || (mix_mode == 2 && !lam))) return UB_ERR_ARG;
     ConvIn in = {x, ldx, part_stride, n_parts, col_off, bias};
+    if (update_state && taps < 2) update_state = 0;
     const dim3 grid(n_tokens, (C + 255) / 256), block(256);
+    const dim3 tgrid((n_tokens + CONV_TILE - 1) / CONV_TILE, (C + 255) / 256);
+    // few tokens, or one a sequence: a thread a (token, channel), since a walk over tokens that all take the long way is slow
+    const bool tiled = !update_state && n_tokens >= 4 * CONV_TILE;
     cudaError_t e;
-#define GO(TX, TO) e = ub_launch_dependent(causal_conv_kernel<TX, TO>, grid, block, 0, st, in, w, state, tok_seq, seq_start, seq_slot, \
-                                           (TO*)out, ldo, n_tokens, C, taps, add_input, act, mix_mode, mix_lo, mix_hi, lam, shared, out_bias)
+#define ARGS(TO) in, w, state, update_state, tok_seq, seq_start, seq_slot, (TO*)out, ldo, n_tokens, C
+#define TAIL add_input, act, mix_mode, mix_lo, mix_hi, lam, shared, out_bias
+#define GO(TX, TO) do { \
+        if (!tiled) e = ub_launch_dependent(causal_conv_kernel<TX, TO>, grid, block, 0, st, ARGS(TO), taps, TAIL); \
+        else if (taps == 2) e = ub_launch_dependent(causal_conv_tile_kernel<TX, TO, 1>, tgrid, block, 0, st, ARGS(TO), TAIL); \
+        else if (taps == 3) e = ub_launch_dependent(causal_conv_tile_kernel<TX, TO, 2>, tgrid, block, 0, st, ARGS(TO), TAIL); \
+        else if (taps == 4) e = ub_launch_dependent(causal_conv_tile_kernel<TX, TO, 3>, tgrid, block, 0, st, ARGS(TO), TAIL); \
+        else e = ub_launch_dependent(causal_conv_kernel<TX, TO>, grid, block, 0, st, ARGS(TO), taps, TAIL); } while (0)
     if (x_dtype == UB_F32 && out_dtype == UB_F32) GO(float, float);
     else if (x_dtype == UB_F32 && out_dtype == UB_BF16) GO(float, __nv_bfloat16);
     else if (x_dtype == UB_BF16 && out_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16);
     else if (x_dtype == UB_BF16 && out_dtype == UB_F32) GO(__nv_bfloat16, float);
     else return UB_ERR_UNSUPPORTED;
 #undef GO
+#undef ARGS
+#undef TAIL
     return (int)e;
 }
 

@@ -426,62 +426,116 @@ UB_API int ub_ssm_finish(const float* y, const float* p, long long ldp, int n_pa
 // The selective scan with a decay for every (channel, state element) (the first Mamba form).  For channel c with the step
 // size dt = softplus(dtp + dt_bias[c]), the input x (convolved, activated), and the token's B and C rows of N numbers:
 //     S[c, n] <- exp(dt A[c, n]) S[c, n] + dt x B[n];    y = sum_n S[c, n] C[n] + D[c] x;    out = y * silu(z)
-// A = -exp(A_log) is made once at load.  Four lanes hold one channel's N state elements (NR = ceil(N / 4) each, element
-// n with lane n % 4), tokens are taken in order, a channel's state stays in registers for the step.  Everything is float32;
-// x comes in the activation type (it is a convolution's output), z as float32 sums of the input product's K slices.
+// A = -exp(A_log) is made once at load.  A block of 128 threads takes 128 / LANES channels of one sequence; LANES lanes
+// hold one channel's N state elements (NR = ceil(N / LANES) each, element n with lane n % LANES) in registers for the step.  Tokens
+// come through shared memory a stage at a time: while one stage is worked on, the next one's B and C rows and the
+// channels' dt, x and z are on their way from global memory into registers (softplus and the gate's SiLU are taken
+// there, off the chain from token to token), and a stage's results leave in whole rows.  Everything is float32; x comes
+// in the activation type (it is a convolution's output), z as float32 sums of the input product's K slices.
 // ---------------------------------------------------------------------------------------
-template <typename TX, typename TO, int NR>
+template <typename TX, int LANES, int NR>
 __global__ void __launch_bounds__(128)
 mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, const float* __restrict__ dt_bias,
                    const float* __restrict__ bc, long long ldbc, int b_off, int c_off, const float* __restrict__ A,
                    const float* __restrict__ Dskip, const float* __restrict__ z, long long ldz, int z_parts, long long z_part_stride,
-                   TO* __restrict__ out, float* __restrict__ S, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                   TX* __restrict__ out, float* __restrict__ S, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                    int inner, int N) {
+    constexpr int CH = 128 / LANES;                        // channels a block
+    constexpr int NS = LANES * NR;                         // state elements, padded
+    constexpr int TT = NS <= 32 ? 16 : 8;                  // tokens a stage
+    constexpr int ROW = 2 * NS + 3 * CH;                   // a token in shared memory: B, C, then dt, x and the gate of the channels
+    constexpr int PER = (TT * ROW + 127) / 128;
+    __shared__ float sm[2][TT][ROW];
+    __shared__ float sy[TT][CH];
     pdl_trigger();
     pdl_wait();
-    const int b = blockIdx.y;
-    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 2, q = threadIdx.x & 3;
+    const int tid = threadIdx.x, cl = tid / LANES, q = tid % LANES;
+    const int b = blockIdx.y, c0 = blockIdx.x * CH, c = c0 + cl;
     const int t0 = seq_start[b], t1 = seq_start[b + 1];
-    if (c >= inner || t0 >= t1) return;                    // (the four lanes of a channel leave together)
-    const unsigned lanes = __activemask();
+    if (t0 >= t1) return;
     float* Sc = S + ((long long)seq_slot[b] * inner + c) * N;
     float s[NR], a[NR];
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
-        const int n = i * 4 + q;
-        s[i] = n < N ? Sc[n] : 0.f;
-        a[i] = n < N ? A[(long long)c * N + n] : 0.f;
+        const int n = i * LANES + q;
+        const bool in = c < inner && n < N;
+        s[i] = in ? Sc[n] : 0.f;
+        a[i] = in ? A[(long long)c * N + n] * 1.4426950408889634f : 0.f;      // powers of two
     }
-    const float bias = dt_bias[c], dsk = Dskip[c];
-    for (long long t = t0; t < t1; ++t) {
-        const float pre = dtp[t * inner + c] + bias;
-        const float dt = pre > 20.f ? pre : log1pf(expf(pre));
-        const float xv = to_f32<TX>(x[t * inner + c]);
-        const float dx = dt * xv;
-        const float* Bt = bc + t * ldbc + b_off;
-        const float* Ct = bc + t * ldbc + c_off;
-        float y = 0.f;
+    const float dsk = c < inner ? Dskip[c] : 0.f;
+    float reg[PER];
+    auto fetch = [&](int base) {                           // a stage's numbers on their way into registers: loads only
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = tid + i * 128;
+            const int tt = e / ROW, j = e % ROW;
+            const long long t = (long long)base + tt;
+            float v = 0.f;
+            if (tt < TT && t < t1) {
+                if (j < 2 * NS) {
+                    const int n = j < NS ? j : j - NS;
+                    if (n < N) v = bc[t * ldbc + (j < NS ? b_off : c_off) + n];
+                } else {
+                    const int k = j - 2 * NS, cc = c0 + k % CH;
+                    if (cc < inner) {
+                        if (k < CH) v = dtp[t * inner + cc] + dt_bias[cc];
+                        else if (k < 2 * CH) v = to_f32<TX>(x[t * inner + cc]);
+                        else for (int p = 0; p < z_parts; ++p) v += z[p * z_part_stride + t * ldz + cc];
+                    }
+                }
+            }
+            reg[i] = v;
+        }
+    };
+    auto stash = [&](int buf) {                            // ... and into shared memory, the step size through softplus, the gate through SiLU
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = tid + i * 128;
+            if (e >= TT * ROW) continue;
+            const int k = e % ROW - 2 * NS;
+            float v = reg[i];
+            if (k >= 0 && k < CH) v = v > 20.f ? v : log1pf(expf(v));
+            else if (k >= 2 * CH) v = v / (1.0f + expf(-v));
+            (&sm[buf][0][0])[e] = v;
+        }
+    };
+    fetch(t0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int base = t0; base < t1; base += TT, buf ^= 1) {
+        const int n_tok = min(TT, t1 - base);
+        const bool more = base + TT < t1;
+        if (more) fetch(base + TT);
+        for (int tt = 0; tt < n_tok; ++tt) {
+            const float* row = sm[buf][tt];
+            const float dt = row[2 * NS + cl], xv = row[2 * NS + CH + cl];
+            const float dx = dt * xv;
+            float y = 0.f;
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+                const int n = i * LANES + q;
+                s[i] = fmaf(exp2f(dt * a[i]), s[i], dx * row[n]);
+                y = fmaf(s[i], row[NS + n], y);
+            }
+#pragma unroll
+            for (int o = 1; o < LANES; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (q == 0) sy[tt][cl] = fmaf(dsk, xv, y) * row[2 * NS + 2 * CH + cl];
+        }
+        if (more) stash(buf ^ 1);                          // (that buffer's readers passed the barrier at the end of the last round)
+        __syncthreads();
+        for (int e = tid; e < n_tok * CH; e += 128) {
+            const int tt = e / CH, k = e % CH;
+            if (c0 + k < inner) out[(long long)(base + tt) * inner + c0 + k] = from_f32<TX>(sy[tt][k]);
+        }
+        __syncthreads();
+    }
+    if (c < inner) {
 #pragma unroll
         for (int i = 0; i < NR; ++i) {
-            const int n = i * 4 + q;
-            if (n < N) {
-                s[i] = fmaf(expf(dt * a[i]), s[i], dx * Bt[n]);
-                y = fmaf(s[i], Ct[n], y);
-            }
+            const int n = i * LANES + q;
+            if (n < N) Sc[n] = s[i];
         }
-        y += __shfl_xor_sync(lanes, y, 1);
-        y += __shfl_xor_sync(lanes, y, 2);
-        if (q == 0) {
-            float zv = 0.f;
-            for (int i = 0; i < z_parts; ++i) zv += z[i * z_part_stride + t * ldz + c];
-            y = fmaf(dsk, xv, y);
-            out[t * inner + c] = from_f32<TO>(y * zv / (1.0f + expf(-zv)));
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < NR; ++i) {
-        const int n = i * 4 + q;
-        if (n < N) Sc[n] = s[i];
     }
 }
 
@@ -491,16 +545,20 @@ UB_API int ub_mamba1_scan(const void* x, int x_dtype, const float* dtp, const fl
                           int n_seqs, int n_tokens, int inner, int N, cudaStream_t st) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (inner <= 0 || N <= 0 || N > 256 || n_seqs > 65535 || z_parts < 1 || x_dtype != out_dtype) return UB_ERR_ARG;
-    const dim3 grid((unsigned)((inner * 4 + 127) / 128), n_seqs), block(128);
-    const int nr = (N + 3) / 4;
-    // a step of more than one token a sequence starts behind the end of the kernels before it (its blocks are busy for the
-    // whole step and should each find a multiprocessor with room), as the other scans do
+    // lanes a channel: four for the smallest states, else sixteen (more warps with shorter chains: the kernel is bound by
+    // the chain from token to token, not by bytes)
+    const int lanes = N <= 4 ? 4 : 16;
+    const int ch = 128 / lanes;
+    const dim3 grid((unsigned)((inner + ch - 1) / ch), n_seqs), block(128);
+    const int nr = (N + lanes - 1) / lanes;
+    // a step of more than one token a sequence starts behind the end of the kernels before it, as the other scans do
     const bool dep = n_tokens <= n_seqs;
     cudaError_t e = cudaErrorInvalidValue;
-#define GO3(TX, NRR) e = ub_launch_ordered(dep, mamba1_scan_kernel<TX, TX, NRR>, grid, block, 0, st, (const TX*)x, dtp, dt_bias, bc, ldbc, b_off, \
-                                           c_off, A, Dskip, z, ldz, z_parts, z_part_stride, (TX*)out, S, seq_start, seq_slot, inner, N)
-#define GO(NRR) do { if (x_dtype == UB_F32) GO3(float, NRR); else if (x_dtype == UB_BF16) GO3(__nv_bfloat16, NRR); else return UB_ERR_UNSUPPORTED; } while (0)
-    if (nr <= 2) GO(2); else if (nr <= 4) GO(4); else if (nr <= 8) GO(8); else if (nr <= 16) GO(16); else if (nr <= 32) GO(32); else GO(64);
+#define GO3(TX, LL, NRR) e = ub_launch_ordered(dep, mamba1_scan_kernel<TX, LL, NRR>, grid, block, 0, st, (const TX*)x, dtp, dt_bias, bc, ldbc, b_off, \
+                                               c_off, A, Dskip, z, ldz, z_parts, z_part_stride, (TX*)out, S, seq_start, seq_slot, inner, N)
+#define GO(LL, NRR) do { if (x_dtype == UB_F32) GO3(float, LL, NRR); else if (x_dtype == UB_BF16) GO3(__nv_bfloat16, LL, NRR); else return UB_ERR_UNSUPPORTED; } while (0)
+    if (lanes == 4) GO(4, 1);
+    else if (nr <= 1) GO(16, 1); else if (nr <= 2) GO(16, 2); else if (nr <= 4) GO(16, 4); else if (nr <= 8) GO(16, 8); else GO(16, 16);
 #undef GO
 #undef GO3
     return (int)e;

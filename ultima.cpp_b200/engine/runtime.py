@@ -123,17 +123,28 @@ class Runtime:
             raise RuntimeError("a wait inside a kernel ran out of time; the step's results are not valid")
 
     # ---- products ----------------------------------------------------------------------
-    def matmul(self, a, w, out, epilogue=ops.EPI_STORE, w2=None, gate=None):
+    def matmul(self, a, w, out, epilogue=ops.EPI_STORE, w2=None, gate=None, unary=0):
         """out (=, +=) a @ w.T with float32 accumulation; see kernels.ops for the epilogues.  ``gate`` =
-        (limit, alpha, shift): the constants of a clamped gate product (tensor-core epilogues only)."""
+        (limit, alpha, shift): the constants of a clamped gate product (tensor-core epilogues only).  ``unary``
+        (ops.UNARY_*): out = f(a @ w.T), the function taken of the float32 sums: in the tensor-core product's storing
+        epilogue, elsewhere by a kernel behind the product."""
         self.launches += 1
+        if unary and (epilogue != ops.EPI_STORE or gate is not None):
+            raise ops.KernelError("a function of the sums goes with the storing epilogue")
         if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
             from ..kernels import gemm_tc
+            if unary:
+                gate = gemm_tc.unary_constants(unary)
             key = gemm_tc.launch_key(a, w, out, epilogue, w2, self._status_ptr, gate)
             if gemm_tc.relaunch(key):
                 return None
             if gemm_tc.accepts(a, w, out, epilogue, w2):
                 return gemm_tc.gemm(a, w, out, epilogue, w2, self, key=key, gate=gate)
+        if unary:
+            sums = self.arena.alloc(tuple(out.shape), torch.float32)
+            ops.gemm_simt(a, w, sums)
+            self.launches += 1
+            return ops.unary(sums, out, unary)
         if gate is not None:
             raise ops.KernelError("a clamped gate product is an epilogue of the tensor-core product only")
         if epilogue == ops.EPI_SWIGLU_IL:
@@ -169,15 +180,21 @@ class Runtime:
                 return gemm_tc.batched(a, w, out, self)
         return ops.gemm_batched(a, w, out)
 
-    def matmul_grouped(self, a, w, out, plan, epilogue=ops.EPI_STORE, w2=None):
+    def matmul_grouped(self, a, w, out, plan, epilogue=ops.EPI_STORE, w2=None, unary=0):
         """Sorted rows against the matrix their tile names (``plan``: a routed feed-forward's ``RoutePlan``):
         out[p] = a[plan.src_rows[p] or p] @ w[e].T, e the expert of the tile that holds sorted row p.  The tensor-core
         product takes rows that lie in the sorted order already (``plan.gather`` False); ``grouped_on_tensor_cores``
-        says beforehand whether it will take a product."""
+        says beforehand whether it will take a product.  ``unary`` (ops.UNARY_*): out = f(product), as in ``matmul``."""
         self.launches += 1
         if not plan.gather and self.grouped_on_tensor_cores(a, w, out, epilogue, w2):
             from ..kernels import gemm_tc
-            return gemm_tc.grouped(a, w, out, plan, epilogue, w2, self)
+            return gemm_tc.grouped(a, w, out, plan, epilogue, w2, self, unary=unary)
+        if unary:
+            sums = self.arena.alloc(tuple(out.shape), torch.float32)
+            ops.gemm_grouped(a, w, sums, plan.tiles, plan.n_tiles, plan.src_rows if plan.gather else None, plan.max_tiles,
+                             epilogue, w2)
+            self.launches += 1
+            return ops.unary(sums, out, unary)
         return ops.gemm_grouped(a, w, out, plan.tiles, plan.n_tiles, plan.src_rows if plan.gather else None, plan.max_tiles,
                                 epilogue, w2)
 

@@ -34,7 +34,7 @@ def lib():
         L.ub_gemm_tc_pair.restype = c_int
         L.ub_gemm_tc_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
                                          c_int, c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_longlong, c_void_p,
-                                         c_void_p]
+                                         c_void_p, c_void_p]
         L.ub_gemm_tc_grouped.restype = c_int
         L.ub_gemm_tc_set_pdl.argtypes = [c_int]
         L.ub_gemm_tc_set_pdl.restype = None
@@ -146,7 +146,7 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
     """out: [T, N]; for EPI_SWIGLU_IL [T, N / 2]; for EPI_STORE with ``splits`` > 1 a float32
     [splits, T, N] whose sum over the first axis is the product.  ``gate`` = (limit, alpha, shift): the gate
     product of the two SWIGLU epilogues becomes g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit) and
-    u' = clamp(u, -limit, limit); None: silu(g) u."""
+    u' = clamp(u, -limit, limit); None: silu(g) u.  A fourth number is EPI_STORE's function of the sum (see ``unary_constants``)."""
     T, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.stride(-1) == 1
@@ -162,7 +162,7 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
         assert s == 1 or epilogue == EPI_ADD
         ldo = out.stride(0)
     L = lib()
-    consts = (ctypes.c_float * 3)(*[float(v) for v in gate]) if gate is not None else None
+    consts = (ctypes.c_float * 4)(*([float(v) for v in gate] + [0.0])[:4]) if gate is not None else None
     if not tile_given and out.dim() == 2 and pairs(T, N, s, epilogue):
         fn, what = L.ub_gemm_tc_pair, "gemm_tc_pair"
         maps = (_tmap_entry(w, 128), _tmap_entry(a, 128))
@@ -260,7 +260,13 @@ def accepts_grouped(a, w, out, epilogue, w2=None) -> bool:
     return epilogue == EPI_STORE and out.dtype in (torch.bfloat16, torch.float32)
 
 
-def grouped(a, w, out, plan, epilogue, w2, rt):
+def unary_constants(kind: int):
+    """The constants that make a storing product store a function of its sums: 1 the exact GELU, 2 the squared rectifier
+    (whole K only); they travel where a gate product's constants do."""
+    return (float("inf"), 1.0, 0.0, float(kind))
+
+
+def grouped(a, w, out, plan, epilogue, w2, rt, unary: int = 0):
     """out[p] = a[p] @ w[e].T for the sorted rows p of every tile (e, first row, rows) of ``plan``; a [rows, K] lies in
     the sorted order already.  ``plan.tile`` is the most rows a tile has (16 to 128)."""
     E, N, K = w.shape
@@ -269,7 +275,8 @@ def grouped(a, w, out, plan, epilogue, w2, rt):
     bn = int(plan.tile)
     rc = lib().ub_gemm_tc_grouped(_tmap(wv, 128), m2, _tmap(a, bn), _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
                                   out.stride(0), a.shape[0], N, K, bn, epilogue, _ptr(plan.tiles), _ptr(plan.n_tiles),
-                                  int(plan.max_tiles), E, step, 0, 0, _ptr(rt.status[1:2]), _stream())
+                                  int(plan.max_tiles), E, step, 0, 0, _ptr(rt.status[1:2]),
+                                  (ctypes.c_float * 4)(*unary_constants(unary)) if unary else None, _stream())
     _check(rc, "gemm_tc_grouped")
 
 
@@ -292,5 +299,5 @@ def batched(a, w, out, rt):
     bn = min(bn, 128)
     rc = lib().ub_gemm_tc_grouped(_tmap(wv, 128), 0, _tmap(a2, bn), _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
                                   out.stride(0), T, N, K, bn, EPI_STORE, None, None, 0, B, step, a.stride(1), out.stride(1),
-                                  _ptr(rt.status[1:2]), _stream())
+                                  _ptr(rt.status[1:2]), None, _stream())
     _check(rc, "gemm_tc_batched")

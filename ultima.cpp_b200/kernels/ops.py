@@ -143,7 +143,7 @@ def _declare(lib, source: str) -> None:
                    "ub_mamba1_scan": [P, I, P, P, P, L, I, I, P, P, P, L, I, L, P, I, P, P, P, I, I, I, I, P]},
         "rowwise.cu": {"ub_layernorm": [P, P, P, I, P, I, I, F, P],
                        "ub_scale_add_norm": [P, P, P, I, P, F, P, I, I, I, I, P],
-                       "ub_causal_conv": [P, I, L, I, L, I, P, P, P, P, P, P, P, I, L, I, I, I, I, I, I, I, I, P, P, P, P],
+                       "ub_causal_conv": [P, I, L, I, L, I, P, P, P, I, P, P, P, P, I, L, I, I, I, I, I, I, I, I, P, P, P, P],
                        "ub_causal_conv_state": [P, I, L, I, L, I, P, P, P, P, I, I, I, P],
                        "ub_take_cols": [P, L, I, L, I, I, I, P, I, L, I, I, P],
                        "ub_unary": [P, I, P, I, L, I, P],
@@ -838,14 +838,16 @@ def _conv_in(x, col_off, n_cols):
     return x.shape[0], x.stride(0), 1, 0
 
 
-def causal_conv(x, w, state, batch, out, col_off=0, bias=None, add_input=False, silu=False, mix=None, out_bias=None):
+def causal_conv(x, w, state, batch, out, col_off=0, bias=None, add_input=False, silu=False, mix=None, out_bias=None,
+                update_state=False):
     """A short causal convolution over time on ``C = out.shape[1]`` channels of x (columns from ``col_off`` on; x [T, N] or
     [parts, T, N], summed; ``bias`` [C] is added to every input first): out_t = sum_j w[:, j] u_(t - taps + 1 + j), with the
     inputs of before the step from ``state`` float32 [slots, taps - 1, C] and zeros before a sequence's start.  ``w`` None:
     no convolution (out = u).  ``add_input``: out = u + conv(u).  ``out_bias`` [C]: added to the result (a bias of the
     convolution, which the state does not hold).  ``silu``: through SiLU.  ``mix`` = (mode, lo, hi, lam,
     shared): the channels lo .. hi - 1 go out to ``shared`` float32 [T, hi - lo] (mode 1) or become (1 - lam) * own +
-    lam * shared (mode 2; lam a float32 scalar on the device).  The state is not moved on: ``causal_conv_state`` does that."""
+    lam * shared (mode 2; lam a float32 scalar on the device).  The state is moved on by ``causal_conv_state``, or here with
+    ``update_state`` when every sequence brings ONE token (a channel's state then has one reader)."""
     _need_cuda(x, w, state, out, bias, out_bias)
     assert out_bias is None or (out_bias.dtype == torch.float32 and out_bias.is_contiguous() and out_bias.numel() == out.shape[1])
     C = out.shape[1]
@@ -856,6 +858,8 @@ def causal_conv(x, w, state, batch, out, col_off=0, bias=None, add_input=False, 
     assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C)
     if taps > 1:
         assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, C)
+    if update_state:
+        assert batch.n_seqs == T, "the state moves on in this kernel only when every sequence brings one token"
     mode, lo, hi, lam, shared = mix if mix is not None else (0, 0, 0, None, None)
     if mode:
         _need_cuda(lam, shared)
@@ -863,7 +867,7 @@ def causal_conv(x, w, state, batch, out, col_off=0, bias=None, add_input=False, 
         assert lam is None or (lam.dtype == torch.float32 and lam.numel() == 1)
     _check(_lib("rowwise.cu").ub_causal_conv(
         _ptr(x), _code(x), ldx, n_parts, part_stride, int(col_off), _ptr(bias), _ptr(w), _ptr(state) if taps > 1 else 0,
-        _ptr(batch.tok_seq), _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(out), _code(out), out.stride(0), T, C, taps,
+        1 if (update_state and taps > 1) else 0, _ptr(batch.tok_seq), _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(out), _code(out), out.stride(0), T, C, taps,
         1 if add_input else 0, 1 if silu else 0, int(mode), int(lo), int(hi), _ptr(lam), _ptr(shared), _ptr(out_bias),
         _stream()), "causal_conv")
 

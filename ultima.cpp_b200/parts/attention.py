@@ -324,9 +324,10 @@ class Attention(Mixer):
             first = rt.carry(("value_mix", self.value_mix_key), T, self.v_width, torch.float32)
             mix = (1 if self.value_mix == "source" else 2, self.q_width + self.kv_width, C, self.lam, first)
         state = cache.states[0] if self.conv > 1 else None
+        one_each = batch.max_new == 1 and batch.n_seqs == T           # one token a sequence: the kernel moves the state on itself
         rt.launches += 1
-        ops.causal_conv(x, self.conv_w, state, batch, out, bias=self.bias_qkv, mix=mix)
-        if self.conv > 1:
+        ops.causal_conv(x, self.conv_w, state, batch, out, bias=self.bias_qkv, mix=mix, update_state=one_each)
+        if self.conv > 1 and not one_each:
             rt.launches += 1
             ops.causal_conv_state(x, state, batch, bias=self.bias_qkv)
         return out

@@ -113,9 +113,10 @@ class CausalConvResidual(InputFilter):
     def forward(self, h, batch, cache, rt):
         out = rt.arena.alloc(tuple(h.shape), h.dtype)
         state = cache.states[0] if self.taps > 1 else None
+        one_each = batch.max_new == 1 and batch.n_seqs == h.shape[0]      # one token a sequence: the kernel moves the state on itself
         rt.launches += 1
-        ops.causal_conv(h, self.w, state, batch, out, add_input=True)
-        if self.taps > 1:
+        ops.causal_conv(h, self.w, state, batch, out, add_input=True, update_state=one_each)
+        if self.taps > 1 and not one_each:
             rt.launches += 1
             ops.causal_conv_state(h, state, batch)
         return out

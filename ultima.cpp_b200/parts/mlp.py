@@ -118,7 +118,7 @@ _ACTIVATIONS = {"gelu_erf": ops.UNARY_GELU_ERF, "relu_squared": ops.UNARY_RELU_S
 class PlainMLP(FeedForward):
     """down(act(up(h))), no gate and no biases, added to the stream it is handed; ``activation`` is "gelu_erf" (the exact
     GELU, 0.5 z (1 + erf(z / sqrt 2))) or "relu_squared" (max(z, 0)^2).  The activation is float32 arithmetic on the up
-    product's float32 sums, rounded once to the activation type."""
+    product's float32 sums, rounded once to the activation type: on the tensor cores in the product's epilogue."""
 
     graph_safe = True
 
@@ -140,9 +140,6 @@ class PlainMLP(FeedForward):
 
     def forward(self, h, residual, batch, rt):
         T = h.shape[0]
-        u = rt.arena.alloc((T, self.inner), torch.float32)
-        rt.matmul(h, self.wu, u)
         a = rt.arena.alloc((T, self.inner), rt.dtype)
-        rt.launches += 1
-        ops.unary(u, a, _ACTIVATIONS[self.activation])
+        rt.matmul(h, self.wu, a, unary=_ACTIVATIONS[self.activation])       # the activation in the product's epilogue
         rt.matmul(a, self.wd, residual, ops.EPI_ADD)

@@ -141,7 +141,8 @@ class RoutedExperts(FeedForward):
             w_gate, w_up = self.w_gu[:, :self.inner], self.w_gu[:, self.inner:]
             first = (w_gate, act, ops.EPI_SWIGLU, w_up)
         else:
-            first = (self.w_gu, rt.arena.alloc((T * top, self.inner), f32), ops.EPI_STORE, None)     # the up product's sums
+            first = (self.w_gu, act, ops.EPI_STORE, None)          # the squared rectifier in the up product's epilogue
+        unary = 0 if self.gated else ops.UNARY_RELU_SQUARED
         # the tensor-core products take both or neither: their tiles are cut to the rows an expert gets on average
         fast = (rt.grouped_on_tensor_cores(h, first[0], first[1], first[2], first[3])
                 and rt.grouped_on_tensor_cores(act, self.w_down, y))
@@ -167,12 +168,9 @@ class RoutedExperts(FeedForward):
             rt.launches += 1
             ops.route_gather(h, row_pos, rows)
             plan.gather = False
-            rt.matmul_grouped(rows, first[0], first[1], plan, first[2], w2=first[3])
+            rt.matmul_grouped(rows, first[0], first[1], plan, first[2], w2=first[3], unary=unary)
         else:
-            rt.matmul_grouped(h, first[0], first[1], plan, first[2], w2=first[3])
-        if not self.gated:
-            rt.launches += 1
-            ops.unary(first[1], act, ops.UNARY_RELU_SQUARED)
+            rt.matmul_grouped(h, first[0], first[1], plan, first[2], w2=first[3], unary=unary)
         plan.gather = False
         rt.matmul_grouped(act, self.w_down, y, plan)
         rt.launches += 1

@@ -180,9 +180,10 @@ class SelectiveScan(Mixer):
             p = rt.arena.alloc((T, 2 * self.inner), f32)
             rt.matmul(h, self.w_in, p)
         xc = rt.arena.alloc((T, self.inner), rt.dtype)
+        one_each = batch.max_new == 1 and batch.n_seqs == T           # one token a sequence: the kernel moves the state on itself
         rt.launches += 1
-        ops.causal_conv(p, self.conv_w, conv_state, batch, xc, silu=True, out_bias=self.conv_b)
-        if self.conv > 1:
+        ops.causal_conv(p, self.conv_w, conv_state, batch, xc, silu=True, out_bias=self.conv_b, update_state=one_each)
+        if self.conv > 1 and not one_each:
             rt.launches += 1
             ops.causal_conv_state(p, conv_state, batch)
         bc = rt.arena.alloc((T, self.dt_rank + 2 * self.n_state), f32)
