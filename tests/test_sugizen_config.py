@@ -100,5 +100,6 @@ def test_a_run_with_two_states_gets_both_and_they_start_at_zero():
     assert tuple(g.k.shape[2:]) == (2, 64, 8) and tuple(g.v.shape[2:]) == (2, 64, 4)
     shared = cache.run_cache(2, [torch.zeros(1, 2, dtype=torch.int32)])
     assert shared.kv is not None and not shared.kv.owner and shared.kv.k.data_ptr() == g.k[0].data_ptr()
-    with pytest.raises(Exception):
-        Cache([(a, a)], [None], 64, 64, 1, 64)
+    # a run may name the same need twice (two convolutions over channels of one width): two arrays of one group
+    twice = Cache([(a, a)], [None], 64, 64, 1, 64).run_cache(0, [])
+    assert len(twice.states) == 2 and twice.states[0].data_ptr() != twice.states[1].data_ptr()

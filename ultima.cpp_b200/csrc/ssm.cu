@@ -445,8 +445,9 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
     constexpr int TT = NS <= 32 ? 16 : 8;                  // tokens a stage
     constexpr int ROW = 2 * NS + 3 * CH;                   // a token in shared memory: B, C, then dt, x and the gate of the channels
     constexpr int PER = (TT * ROW + 127) / 128;
+    constexpr int U = NR <= 4 ? 4 : 2;                     // tokens whose decays are formed together
     __shared__ float sm[2][TT][ROW];
-    __shared__ float sy[TT][CH];
+    __shared__ float sp[TT][128];                          // a lane's share of a token's read-out
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, cl = tid / LANES, q = tid % LANES;
@@ -462,7 +463,6 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
         s[i] = in ? Sc[n] : 0.f;
         a[i] = in ? A[(long long)c * N + n] * 1.4426950408889634f : 0.f;      // powers of two
     }
-    const float dsk = c < inner ? Dskip[c] : 0.f;
     float reg[PER];
     auto fetch = [&](int base) {                           // a stage's numbers on their way into registers: loads only
 #pragma unroll
@@ -487,46 +487,68 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
             reg[i] = v;
         }
     };
-    auto stash = [&](int buf) {                            // ... and into shared memory, the step size through softplus, the gate through SiLU
+    auto stash = [&](int buf, int base) {                  // ... and into shared memory, the step size through softplus, the gate through SiLU
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int e = tid + i * 128;
             if (e >= TT * ROW) continue;
             const int k = e % ROW - 2 * NS;
             float v = reg[i];
-            if (k >= 0 && k < CH) v = v > 20.f ? v : log1pf(expf(v));
+            if (base + e / ROW >= t1) v = 0.f;             // past the sequence's end: a step size of zero leaves the state as it is
+            else if (k >= 0 && k < CH) v = v > 20.f ? v : log1pf(expf(v));
             else if (k >= 2 * CH) v = v / (1.0f + expf(-v));
             (&sm[buf][0][0])[e] = v;
         }
     };
     fetch(t0);
-    stash(0);
+    stash(0, t0);
     __syncthreads();
     int buf = 0;
     for (int base = t0; base < t1; base += TT, buf ^= 1) {
         const int n_tok = min(TT, t1 - base);
         const bool more = base + TT < t1;
         if (more) fetch(base + TT);
-        for (int tt = 0; tt < n_tok; ++tt) {
-            const float* row = sm[buf][tt];
-            const float dt = row[2 * NS + cl], xv = row[2 * NS + CH + cl];
-            const float dx = dt * xv;
-            float y = 0.f;
+        // Tokens past the sequence's end are zeros in shared memory (decay 1, nothing written), so a stage is always walked
+        // whole.  Four tokens at a time: their decays and inputs first (independent of one another), then the chain from
+        // token to token, which is one multiply-add a state element; a lane's share of the read-out goes to shared memory
+        // and is summed over the lanes behind the stage.
 #pragma unroll
-            for (int i = 0; i < NR; ++i) {
-                const int n = i * LANES + q;
-                s[i] = fmaf(exp2f(dt * a[i]), s[i], dx * row[n]);
-                y = fmaf(s[i], row[NS + n], y);
+        for (int t4 = 0; t4 < TT; t4 += U) {
+            float dA[U][NR], in[U][NR];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float* row = sm[buf][t4 + u];
+                const float dt = row[2 * NS + cl];
+                const float dx = dt * row[2 * NS + CH + cl];
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    dA[u][i] = exp2f(dt * a[i]);
+                    in[u][i] = dx * row[i * LANES + q];
+                }
             }
 #pragma unroll
-            for (int o = 1; o < LANES; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (q == 0) sy[tt][cl] = fmaf(dsk, xv, y) * row[2 * NS + 2 * CH + cl];
+            for (int u = 0; u < U; ++u) {
+                const float* row = sm[buf][t4 + u];
+                float y = 0.f;
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    s[i] = fmaf(dA[u][i], s[i], in[u][i]);
+                    y = fmaf(s[i], row[NS + i * LANES + q], y);
+                }
+                sp[t4 + u][tid] = y;                       // [token][channel of the block][lane]
+            }
         }
-        if (more) stash(buf ^ 1);                          // (that buffer's readers passed the barrier at the end of the last round)
+        if (more) stash(buf ^ 1, base + TT);               // (that buffer's readers passed the barrier at the end of the last round)
         __syncthreads();
         for (int e = tid; e < n_tok * CH; e += 128) {
             const int tt = e / CH, k = e % CH;
-            if (c0 + k < inner) out[(long long)(base + tt) * inner + c0 + k] = from_f32<TX>(sy[tt][k]);
+            if (c0 + k >= inner) continue;
+            float y = 0.f;
+#pragma unroll
+            for (int l = 0; l < LANES; ++l) y += sp[tt][k * LANES + l];
+            const float* row = sm[buf][tt];
+            y = fmaf(Dskip[c0 + k], row[2 * NS + CH + k], y) * row[2 * NS + 2 * CH + k];
+            out[(long long)(base + tt) * inner + c0 + k] = from_f32<TX>(y);
         }
         __syncthreads();
     }
