@@ -433,6 +433,13 @@ UB_API int ub_ssm_finish(const float* y, const float* p, long long ldp, int n_pa
 // there, off the chain from token to token), and a stage's results leave in whole rows.  Everything is float32; x comes
 // in the activation type (it is a convolution's output), z as float32 sums of the input product's K slices.
 // ---------------------------------------------------------------------------------------
+// 2^x by the hardware's approximation (about 2^-22 relative): the decay of a state element, taken sixteen times a token and lane
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <typename TX, int LANES, int NR>
 __global__ void __launch_bounds__(128)
 mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, const float* __restrict__ dt_bias,
@@ -447,7 +454,7 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
     constexpr int PER = (TT * ROW + 127) / 128;
     constexpr int U = NR <= 4 ? 4 : 2;                     // tokens whose decays are formed together
     __shared__ float sm[2][TT][ROW];
-    __shared__ float sp[TT][128];                          // a lane's share of a token's read-out
+    __shared__ float sp[TT][CH * (LANES + 1)];             // a lane's share of a token's read-out (a channel's lanes one bank on)
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, cl = tid / LANES, q = tid % LANES;
@@ -463,25 +470,43 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
         s[i] = in ? Sc[n] : 0.f;
         a[i] = in ? A[(long long)c * N + n] * 1.4426950408889634f : 0.f;      // powers of two
     }
+    // What this thread brings into a stage is the same from stage to stage but for the first token: the places are worked
+    // out once (a pointer at token 0, a stride a token, what is done to the number), so that a stage's fetch is loads only.
     float reg[PER];
+    const float* src[PER];                                 // float sources: B, C, the step size's sums, the gate's sums
+    const TX* srcx[PER];                                   // x comes in the activation type
+    long long step[PER];
+    float add[PER];
+    int kind[PER];                                         // 0 nothing to bring, 1 a float as it is, 2 step size (softplus), 3 x, 4 gate (SiLU)
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = tid + i * 128;
+        const int tt = e / ROW, j = e % ROW;
+        src[i] = nullptr; srcx[i] = nullptr; step[i] = 0; add[i] = 0.f; kind[i] = 0;
+        if (tt >= TT) continue;
+        if (j < 2 * NS) {
+            const int n = j < NS ? j : j - NS;
+            if (n < N) { kind[i] = 1; step[i] = ldbc; src[i] = bc + tt * ldbc + (j < NS ? b_off : c_off) + n; }
+        } else {
+            const int k = j - 2 * NS, cc = c0 + k % CH;
+            if (cc < inner) {
+                if (k < CH) { kind[i] = 2; step[i] = inner; src[i] = dtp + (long long)tt * inner + cc; add[i] = dt_bias[cc]; }
+                else if (k < 2 * CH) { kind[i] = 3; step[i] = inner; srcx[i] = x + (long long)tt * inner + cc; }
+                else { kind[i] = 4; step[i] = ldz; src[i] = z + (long long)tt * ldz + cc; }
+            }
+        }
+    }
     auto fetch = [&](int base) {                           // a stage's numbers on their way into registers: loads only
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
-            const int e = tid + i * 128;
-            const int tt = e / ROW, j = e % ROW;
-            const long long t = (long long)base + tt;
+            const int tt = (tid + i * 128) / ROW;
             float v = 0.f;
-            if (tt < TT && t < t1) {
-                if (j < 2 * NS) {
-                    const int n = j < NS ? j : j - NS;
-                    if (n < N) v = bc[t * ldbc + (j < NS ? b_off : c_off) + n];
-                } else {
-                    const int k = j - 2 * NS, cc = c0 + k % CH;
-                    if (cc < inner) {
-                        if (k < CH) v = dtp[t * inner + cc] + dt_bias[cc];
-                        else if (k < 2 * CH) v = to_f32<TX>(x[t * inner + cc]);
-                        else for (int p = 0; p < z_parts; ++p) v += z[p * z_part_stride + t * ldz + cc];
-                    }
+            if (kind[i] && base + tt < t1) {
+                if (kind[i] == 3) v = to_f32<TX>(srcx[i][(long long)base * step[i]]);
+                else {
+                    // (a load the compiler may not move down to where the number is used, behind the stage's arithmetic)
+                    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(src[i] + (long long)base * step[i]));
+                    if (kind[i] == 4) for (int p = 1; p < z_parts; ++p) v += src[i][(long long)base * step[i] + p * z_part_stride];
                 }
             }
             reg[i] = v;
@@ -492,11 +517,10 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
         for (int i = 0; i < PER; ++i) {
             const int e = tid + i * 128;
             if (e >= TT * ROW) continue;
-            const int k = e % ROW - 2 * NS;
             float v = reg[i];
             if (base + e / ROW >= t1) v = 0.f;             // past the sequence's end: a step size of zero leaves the state as it is
-            else if (k >= 0 && k < CH) v = v > 20.f ? v : log1pf(expf(v));
-            else if (k >= 2 * CH) v = v / (1.0f + expf(-v));
+            else if (kind[i] == 2) { v += add[i]; v = v > 20.f ? v : log1pf(expf(v)); }
+            else if (kind[i] == 4) v = v / (1.0f + expf(-v));
             (&sm[buf][0][0])[e] = v;
         }
     };
@@ -522,7 +546,7 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
                 const float dx = dt * row[2 * NS + CH + cl];
 #pragma unroll
                 for (int i = 0; i < NR; ++i) {
-                    dA[u][i] = exp2f(dt * a[i]);
+                    dA[u][i] = fast_exp2(dt * a[i]);
                     in[u][i] = dx * row[i * LANES + q];
                 }
             }
@@ -535,7 +559,7 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
                     s[i] = fmaf(dA[u][i], s[i], in[u][i]);
                     y = fmaf(s[i], row[NS + i * LANES + q], y);
                 }
-                sp[t4 + u][tid] = y;                       // [token][channel of the block][lane]
+                sp[t4 + u][cl * (LANES + 1) + q] = y;      // [token][channel of the block][lane]
             }
         }
         if (more) stash(buf ^ 1, base + TT);               // (that buffer's readers passed the barrier at the end of the last round)
@@ -545,7 +569,7 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
             if (c0 + k >= inner) continue;
             float y = 0.f;
 #pragma unroll
-            for (int l = 0; l < LANES; ++l) y += sp[tt][k * LANES + l];
+            for (int l = 0; l < LANES; ++l) y += sp[tt][k * (LANES + 1) + l];
             const float* row = sm[buf][tt];
             y = fmaf(Dskip[c0 + k], row[2 * NS + CH + k], y) * row[2 * NS + 2 * CH + k];
             out[(long long)(base + tt) * inner + c0 + k] = from_f32<TX>(y);
