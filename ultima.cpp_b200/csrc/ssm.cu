@@ -585,6 +585,181 @@ mamba1_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, cons
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same scan for steps of many tokens a sequence, as three kernels: what is a function of one (token, channel) alone
+// is taken out of the chain from token to token.
+//   mamba1_pre     dt = softplus(dtp + dt_bias) (in place) and dx = dt * x, float32
+//   mamba1_chain   the recurrence over copies (cp.async, two stages in flight) of dt, dx, B and C: per token and state
+//                  element one exponential and three multiply-adds; the sum over the state goes out in float32
+//   mamba1_post    out = (sum + D x) * silu(z)
+// The arithmetic and its order are those of the one-kernel form above.
+// ---------------------------------------------------------------------------------------
+template <typename TX>
+__global__ void mamba1_pre_kernel(float* __restrict__ dtp, const float* __restrict__ dt_bias, const TX* __restrict__ x,
+                                  float* __restrict__ dx, long long n, int inner) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float pre = dtp[i] + dt_bias[i % inner];
+    const float dt = pre > 20.f ? pre : log1pf(expf(pre));
+    dtp[i] = dt;
+    dx[i] = dt * to_f32<TX>(x[i]);
+}
+
+__device__ __forceinline__ void m1_cp4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int LANES, int NR>
+__global__ void __launch_bounds__(128)
+mamba1_chain_kernel(const float* __restrict__ dt, const float* __restrict__ dx, const float* __restrict__ bc, long long ldbc,
+                    int b_off, int c_off, const float* __restrict__ A, float* __restrict__ ysum, float* __restrict__ S,
+                    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int inner, int N) {
+    constexpr int CH = 128 / LANES;
+    constexpr int NS = LANES * NR;
+    constexpr int TT = NS <= 32 ? 16 : 8;
+    constexpr int ROW = 2 * NS + 2 * CH;                   // a token in shared memory: B, C, then dt and dx of the channels
+    constexpr int U = NR <= 4 ? 4 : 2;
+    __shared__ float sm[2][TT][ROW];
+    __shared__ float sp[TT][CH * (LANES + 1)];
+    const int tid = threadIdx.x, cl = tid / LANES, q = tid % LANES;
+    const int b = blockIdx.y, c0 = blockIdx.x * CH, c = c0 + cl;
+    const int t0 = seq_start[b], t1 = seq_start[b + 1];
+    if (t0 >= t1) return;
+    float* Sc = S + ((long long)seq_slot[b] * inner + c) * N;
+    float s[NR], a[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int n = i * LANES + q;
+        const bool in = c < inner && n < N;
+        s[i] = in ? Sc[n] : 0.f;
+        a[i] = in ? A[(long long)c * N + n] * 1.4426950408889634f : 0.f;
+    }
+    auto fetch = [&](int base, int buf) {                  // copies for the tokens there are, zeros behind the sequence's end and past the sizes
+        for (int e = tid; e < TT * ROW; e += 128) {
+            const int tt = e / ROW, j = e % ROW;
+            const long long t = (long long)base + tt;
+            float* dst = &sm[buf][tt][j];
+            const float* src = nullptr;
+            if (t < t1) {
+                if (j < 2 * NS) {
+                    const int n = j < NS ? j : j - NS;
+                    if (n < N) src = bc + t * ldbc + (j < NS ? b_off : c_off) + n;
+                } else {
+                    const int k = j - 2 * NS, cc = c0 + k % CH;
+                    if (cc < inner) src = (k < CH ? dt : dx) + t * inner + cc;
+                }
+            }
+            if (src) m1_cp4(dst, src); else *dst = 0.f;
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(t0, 0);
+    int buf = 0;
+    for (int base = t0; base < t1; base += TT, buf ^= 1) {
+        const int n_tok = min(TT, t1 - base);
+        if (base + TT < t1) {
+            fetch(base + TT, buf ^ 1);                     // (that buffer's readers passed the barrier at the end of the last round)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+#pragma unroll
+        for (int t4 = 0; t4 < TT; t4 += U) {
+            float dA[U][NR], in[U][NR];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float* row = sm[buf][t4 + u];
+                const float dtv = row[2 * NS + cl], dxv = row[2 * NS + CH + cl];
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    dA[u][i] = fast_exp2(dtv * a[i]);
+                    in[u][i] = dxv * row[i * LANES + q];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float* row = sm[buf][t4 + u];
+                float y = 0.f;
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    s[i] = fmaf(dA[u][i], s[i], in[u][i]);
+                    y = fmaf(s[i], row[NS + i * LANES + q], y);
+                }
+                sp[t4 + u][cl * (LANES + 1) + q] = y;
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < n_tok * CH; e += 128) {
+            const int tt = e / CH, k = e % CH;
+            if (c0 + k >= inner) continue;
+            float y = 0.f;
+#pragma unroll
+            for (int l = 0; l < LANES; ++l) y += sp[tt][k * (LANES + 1) + l];
+            ysum[(long long)(base + tt) * inner + c0 + k] = y;
+        }
+        __syncthreads();
+    }
+    if (c < inner) {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int n = i * LANES + q;
+            if (n < N) Sc[n] = s[i];
+        }
+    }
+}
+
+template <typename TX>
+__global__ void mamba1_post_kernel(const float* __restrict__ ysum, const TX* __restrict__ x, const float* __restrict__ Dskip,
+                                   const float* __restrict__ z, long long ldz, int z_parts, long long z_part_stride,
+                                   TX* __restrict__ out, long long n, int inner) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / inner;
+    const int c = (int)(i % inner);
+    float zv = 0.f;
+    for (int p = 0; p < z_parts; ++p) zv += z[p * z_part_stride + t * ldz + c];
+    const float y = fmaf(Dskip[c], to_f32<TX>(x[i]), ysum[i]);
+    out[i] = from_f32<TX>(y * (zv / (1.0f + expf(-zv))));
+}
+
+// work: two float32 arrays [n_tokens, inner] (dx and the sums); dtp is overwritten with the step sizes
+UB_API int ub_mamba1_scan_staged(const void* x, int x_dtype, float* dtp, const float* dt_bias, const float* bc, long long ldbc,
+                                 int b_off, int c_off, const float* A, const float* Dskip, const float* z, long long ldz,
+                                 int z_parts, long long z_part_stride, void* out, int out_dtype, float* S, const int* seq_start,
+                                 const int* seq_slot, int n_seqs, int n_tokens, int inner, int N, float* work, cudaStream_t st) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (inner <= 0 || N <= 0 || N > 256 || n_seqs > 65535 || z_parts < 1 || x_dtype != out_dtype || !work) return UB_ERR_ARG;
+    const long long n = (long long)n_tokens * inner;
+    float* dx = work;
+    float* ysum = work + n;
+    const dim3 egrid((unsigned)((n + 255) / 256)), eblock(256);
+    cudaError_t e;
+    if (x_dtype == UB_F32) e = ub_launch_dependent(mamba1_pre_kernel<float>, egrid, eblock, 0, st, dtp, dt_bias, (const float*)x, dx, n, inner);
+    else if (x_dtype == UB_BF16) e = ub_launch_dependent(mamba1_pre_kernel<__nv_bfloat16>, egrid, eblock, 0, st, dtp, dt_bias, (const __nv_bfloat16*)x, dx, n, inner);
+    else return UB_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return (int)e;
+    const int lanes = N <= 4 ? 4 : 16;
+    const int ch = 128 / lanes;
+    const dim3 grid((unsigned)((inner + ch - 1) / ch), n_seqs), block(128);
+    const int nr = (N + lanes - 1) / lanes;
+    // an ordinary launch, behind the end of the kernels before it: its blocks are busy for the whole step, as the other scans'
+#define GO(LL, NRR) e = ub_launch_ordered(false, mamba1_chain_kernel<LL, NRR>, grid, block, 0, st, (const float*)dtp, (const float*)dx, bc, ldbc, \
+                                          b_off, c_off, A, ysum, S, seq_start, seq_slot, inner, N)
+    if (lanes == 4) GO(4, 1);
+    else if (nr <= 1) GO(16, 1); else if (nr <= 2) GO(16, 2); else if (nr <= 4) GO(16, 4); else if (nr <= 8) GO(16, 8); else GO(16, 16);
+#undef GO
+    if (e != cudaSuccess) return (int)e;
+    if (x_dtype == UB_F32) e = ub_launch_ordered(false, mamba1_post_kernel<float>, egrid, eblock, 0, st, (const float*)ysum, (const float*)x, Dskip, z, ldz, z_parts, z_part_stride, (float*)out, n, inner);
+    else e = ub_launch_ordered(false, mamba1_post_kernel<__nv_bfloat16>, egrid, eblock, 0, st, (const float*)ysum, (const __nv_bfloat16*)x, Dskip, z, ldz, z_parts, z_part_stride, (__nv_bfloat16*)out, n, inner);
+    return (int)e;
+}
+
 UB_API int ub_mamba1_scan(const void* x, int x_dtype, const float* dtp, const float* dt_bias, const float* bc, long long ldbc,
                           int b_off, int c_off, const float* A, const float* Dskip, const float* z, long long ldz, int z_parts,
                           long long z_part_stride, void* out, int out_dtype, float* S, const int* seq_start, const int* seq_slot,

@@ -140,7 +140,8 @@ def _declare(lib, source: str) -> None:
                    "ub_ssm_conv_state_update": [P, L, I, L, P, P, P, P, I, P],
                    "ub_ssm_scan": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
                    "ub_ssm_finish": [P, P, L, I, L, P, P, P, I, I, I, F, F, P],
-                   "ub_mamba1_scan": [P, I, P, P, P, L, I, I, P, P, P, L, I, L, P, I, P, P, P, I, I, I, I, P]},
+                   "ub_mamba1_scan": [P, I, P, P, P, L, I, I, P, P, P, L, I, L, P, I, P, P, P, I, I, I, I, P],
+                   "ub_mamba1_scan_staged": [P, I, P, P, P, L, I, I, P, P, P, L, I, L, P, I, P, P, P, I, I, I, I, P, P]},
         "rowwise.cu": {"ub_layernorm": [P, P, P, I, P, I, I, F, P],
                        "ub_scale_add_norm": [P, P, P, I, P, F, P, I, I, I, I, P],
                        "ub_causal_conv": [P, I, L, I, L, I, P, P, P, I, P, P, P, P, I, L, I, I, I, I, I, I, I, I, P, P, P, P],
@@ -913,11 +914,13 @@ def side_gate(s, table, col0, ids, out, dim):
                                            s.shape[0], _stream()), "side_gate")
 
 
-def mamba1_scan(x, dtp, dt_bias, bc, b_off, c_off, A, d_skip, z, out, state, batch, N):
+def mamba1_scan(x, dtp, dt_bias, bc, b_off, c_off, A, d_skip, z, out, state, batch, N, work=None):
     """The selective scan with a decay for every (channel, state element); see csrc/ssm.cu.  x, out [T, inner] in the
     activation type; dtp float32 [T, inner] (the step size's sums before the bias); bc float32 [T, >= c_off + N] with the B
     row from column b_off and the C row from c_off; A float32 [inner, N] (negative); z float32 [T, M] or [parts, T, M] whose
-    first ``inner`` columns are the gate's sums; state float32 [slots, inner, N]."""
+    first ``inner`` columns are the gate's sums; state float32 [slots, inner, N].  ``work`` (float32 [2, T, inner]): the
+    three-kernel form for steps of many tokens a sequence, which takes what depends on one (token, channel) alone out of the
+    chain from token to token; ``dtp`` is then overwritten with the step sizes."""
     _need_cuda(x, dtp, dt_bias, bc, A, d_skip, z, out, state)
     T, inner = x.shape
     assert x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and x.dtype == out.dtype
@@ -926,6 +929,14 @@ def mamba1_scan(x, dtp, dt_bias, bc, b_off, c_off, A, d_skip, z, out, state, bat
     assert bc.dtype == torch.float32 and bc.stride(1) == 1 and z.dtype == torch.float32
     assert tuple(state.shape[1:]) == (inner, N) and tuple(A.shape) == (inner, N) and tuple(dtp.shape) == (T, inner)
     _, ldz, z_parts, z_stride = _conv_in(z, 0, inner)
+    if work is not None:
+        _need_cuda(work)
+        assert work.dtype == torch.float32 and work.is_contiguous() and work.numel() >= 2 * T * inner
+        _check(_lib("ssm.cu").ub_mamba1_scan_staged(
+            _ptr(x), _code(x), _ptr(dtp), _ptr(dt_bias), _ptr(bc), bc.stride(0), int(b_off), int(c_off), _ptr(A), _ptr(d_skip),
+            _ptr(z), ldz, z_parts, z_stride, _ptr(out), _code(out), _ptr(state), _ptr(batch.seq_start), _ptr(batch.seq_slot),
+            batch.n_seqs, T, inner, int(N), _ptr(work), _stream()), "mamba1_scan_staged")
+        return
     _check(_lib("ssm.cu").ub_mamba1_scan(_ptr(x), _code(x), _ptr(dtp), _ptr(dt_bias), _ptr(bc), bc.stride(0), int(b_off), int(c_off),
                                          _ptr(A), _ptr(d_skip), _ptr(z), ldz, z_parts, z_stride, _ptr(out), _code(out), _ptr(state),
                                          _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, T, inner, int(N), _stream()),

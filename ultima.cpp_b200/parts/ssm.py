@@ -194,8 +194,10 @@ class SelectiveScan(Mixer):
         dtp = rt.arena.alloc((T, self.inner), f32)
         rt.matmul(low, self.w_dt, dtp)
         y = rt.arena.alloc((T, self.inner), rt.dtype)
-        rt.launches += 1
         z = p[..., self.inner:]
+        # many tokens a sequence: softplus, dt * x and the gate leave the chain from token to token (three kernels)
+        work = None if one_each or T < 4 * batch.n_seqs else rt.arena.alloc((2, T, self.inner), f32)
+        rt.launches += 1 if work is None else 3
         ops.mamba1_scan(xc, dtp, self.dt_bias, bc, self.dt_rank, self.dt_rank + self.n_state, self.A, self.d_skip, z, y, S,
-                        batch, self.n_state)
+                        batch, self.n_state, work=work)
         rt.matmul(y, self.wo, residual, ops.EPI_ADD)
