@@ -760,12 +760,60 @@ UB_API int ub_mamba1_scan_staged(const void* x, int x_dtype, float* dtp, const f
     return (int)e;
 }
 
+// One token a sequence: four lanes a (sequence, channel), a lane the state elements n = q, q + 4, ...; nothing is staged.
+template <typename TX>
+__global__ void __launch_bounds__(128)
+mamba1_step_kernel(const TX* __restrict__ x, const float* __restrict__ dtp, const float* __restrict__ dt_bias,
+                   const float* __restrict__ bc, long long ldbc, int b_off, int c_off, const float* __restrict__ A,
+                   const float* __restrict__ Dskip, const float* __restrict__ z, long long ldz, int z_parts, long long z_part_stride,
+                   TX* __restrict__ out, float* __restrict__ S, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                   int inner, int N) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.y, q = threadIdx.x & 3;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 2;
+    const bool live = c < inner;                           // (every lane stays for the exchanges)
+    const long long t = seq_start[b];
+    const int cc = live ? c : 0;
+    const float pre = dtp[t * inner + cc] + dt_bias[cc];
+    const float dt = pre > 20.f ? pre : log1pf(expf(pre));
+    const float xv = to_f32<TX>(x[t * inner + cc]);
+    const float dx = dt * xv;
+    float* Sc = S + ((long long)seq_slot[b] * inner + cc) * N;
+    const float* Ac = A + (long long)cc * N;
+    const float* Bt = bc + t * ldbc + b_off;
+    const float* Ct = bc + t * ldbc + c_off;
+    float y = 0.f;
+    if (live) {
+        for (int n = q; n < N; n += 4) {
+            const float sn = fmaf(fast_exp2(dt * Ac[n] * 1.4426950408889634f), Sc[n], dx * Bt[n]);
+            Sc[n] = sn;
+            y = fmaf(sn, Ct[n], y);
+        }
+    }
+    y += __shfl_xor_sync(0xffffffffu, y, 1);
+    y += __shfl_xor_sync(0xffffffffu, y, 2);
+    if (live && q == 0) {
+        float zv = 0.f;
+        for (int p = 0; p < z_parts; ++p) zv += z[p * z_part_stride + t * ldz + c];
+        out[t * inner + c] = from_f32<TX>(fmaf(Dskip[c], xv, y) * (zv / (1.0f + expf(-zv))));
+    }
+}
+
 UB_API int ub_mamba1_scan(const void* x, int x_dtype, const float* dtp, const float* dt_bias, const float* bc, long long ldbc,
                           int b_off, int c_off, const float* A, const float* Dskip, const float* z, long long ldz, int z_parts,
                           long long z_part_stride, void* out, int out_dtype, float* S, const int* seq_start, const int* seq_slot,
                           int n_seqs, int n_tokens, int inner, int N, cudaStream_t st) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (inner <= 0 || N <= 0 || N > 256 || n_seqs > 65535 || z_parts < 1 || x_dtype != out_dtype) return UB_ERR_ARG;
+    if (n_tokens == n_seqs) {                               // one token a sequence (every sequence of a step brings at least one)
+        const dim3 sgrid((unsigned)((inner * 4 + 127) / 128), n_seqs), sblock(128);
+        cudaError_t e;
+        if (x_dtype == UB_F32) e = ub_launch_dependent(mamba1_step_kernel<float>, sgrid, sblock, 0, st, (const float*)x, dtp, dt_bias, bc, ldbc, b_off, c_off, A, Dskip, z, ldz, z_parts, z_part_stride, (float*)out, S, seq_start, seq_slot, inner, N);
+        else if (x_dtype == UB_BF16) e = ub_launch_dependent(mamba1_step_kernel<__nv_bfloat16>, sgrid, sblock, 0, st, (const __nv_bfloat16*)x, dtp, dt_bias, bc, ldbc, b_off, c_off, A, Dskip, z, ldz, z_parts, z_part_stride, (__nv_bfloat16*)out, S, seq_start, seq_slot, inner, N);
+        else return UB_ERR_UNSUPPORTED;
+        return (int)e;
+    }
     // lanes a channel: four for the smallest states, else sixteen (more warps with shorter chains: the kernel is bound by
     // the chain from token to token, not by bytes)
     const int lanes = N <= 4 ? 4 : 16;
