@@ -183,12 +183,19 @@ causal_conv_tile_kernel(ConvIn in, const float* __restrict__ w, float* __restric
     const bool mixes = mix_mode && c >= mix_lo && c < mix_hi;
     const float l = (mixes && mix_mode == 2) ? *lam : 0.f;
     const long long tbase = (long long)blockIdx.x * CONV_TILE;
+    // the tile's sequence once where the whole tile lies in one (tokens of a sequence stand together, so the first and the
+    // last token tell); a token's input is asked for while the token before it is worked on
+    const int seq0 = tok_seq[tbase];
+    const bool one_seq = tok_seq[min(tbase + CONV_TILE - 1, (long long)n_tokens - 1)] == seq0;
+    const int r0 = (int)tbase - seq_start[seq0];
+    float u_next = conv_input<TX>(in, tbase, c);
     for (int i = 0; i < CONV_TILE; ++i) {
         const long long t = tbase + i;
         if (t >= n_tokens) break;
-        const float u = conv_input<TX>(in, t, c);
-        const int seq = tok_seq[t];
-        const int r = (int)t - seq_start[seq];
+        const float u = u_next;
+        if (i + 1 < CONV_TILE && t + 1 < n_tokens) u_next = conv_input<TX>(in, t + 1, c);
+        const int seq = one_seq ? seq0 : tok_seq[t];
+        const int r = one_seq ? r0 + i : (int)t - seq_start[seq];
         float acc = 0.f;
         if (i >= K && r >= K) {
 #pragma unroll
@@ -265,7 +272,6 @@ UB_API int ub_causal_conv(const void* x, int x_dtype, long long ldx, int n_parts
     if (x_dtype == UB_F32 && out_dtype == UB_F32) GO(float, float);
     else if (x_dtype == UB_F32 && out_dtype == UB_BF16) GO(float, __nv_bfloat16);
     else if (x_dtype == UB_BF16 && out_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16);
-    else if (x_dtype == UB_BF16 && out_dtype == UB_F32) GO(__nv_bfloat16, float);
     else return UB_ERR_UNSUPPORTED;
 #undef GO
 #undef ARGS
