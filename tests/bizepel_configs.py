@@ -78,9 +78,9 @@ WIDE = _model([
     _layer("attention", _attention(8, 2, 64, 64, 0.125, conv=4, rot=(10000.0, 32), mask=(64, 4), v_mix=True), _moe(8, 2, 64, scale=2.0, groups=(4, 2), shared=128)),
     _layer("general_delta", _delta(2, 64, 16), _dense(256)),
     _layer("attention", _attention(2, 2, 128, 128, 0.09, conv=4, rot=(10000.0, 128), mask=(130, 20)), _moe(12, 4, 64, groups=(4, 3))),
-    _layer("mamba1", _mamba(256, 16, 8, 4), _moe(16, 4, 64, scale=2.0, groups=(2, 1), shared=64)),
+    _layer("mamba1", _mamba(256, 16, 8, 4), _moe(20, 5, 64, scale=2.25, groups=(4, 2), shared=64)),
     _layer("attention", _attention(4, 2, 64, 64, 0.125, conv=4, rot=(10000.0, 64), mask=(100, 1), v_mix=True), _dense(256)),
-], vocab=384, width=128, eps=1e-6, taps=4, side=16, logit_scale=2.0)
+], vocab=384, width=128, eps=1e-6, taps=4, side=16, logit_scale=0.75)
 
 # no input convolution, no token input, no logit scale, a layer without feed-forward first
 PLAIN = _model([

@@ -174,7 +174,7 @@ def test_values_handed_from_one_layer_to_another_and_blended():
     assert rel_err(o2, ref) < 1e-6
 
 
-@pytest.mark.parametrize("ne,groups,top,scale", [(6, (3, 2), 2, 1.7), (16, (2, 1), 4, 2.0), (5, None, 3, 1.0), (4, None, 1, 0.5),
+@pytest.mark.parametrize("ne,groups,top,scale", [(6, (3, 2), 2, 1.7), (20, (4, 1), 4, 1.9), (5, None, 3, 1.0), (4, None, 1, 0.5),
                                                  (12, (4, 3), 4, 1.0), (8, (8, 2), 2, 3.0), (64, (8, 3), 6, 2.5), (3, (3, 3), 3, 1.0)])
 def test_the_sigmoid_router_scores_groups_by_their_two_best_and_renormalises(ne, groups, top, scale):
     """The correction is larger than the scores and partly negative, so that choice scores are negative too: an expert
