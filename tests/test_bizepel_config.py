@@ -68,6 +68,8 @@ def test_the_model_as_data_names_every_stored_tensor():
         assert names.get(n) == shape, (n, names.get(n))
     assert "head.weight" not in names and "l4.norm2" not in names and "l4.ls2" not in names
     assert sum(1 for n in names if n == "side.embed") == 1
+    # what a file may carry without the model having a use for it: the second sublayer's tensors of a layer without one
+    assert set(spec.optional_tensors) == {"l4.norm2", "l4.canon2", "l4.ls2"}
     # the first layer that mixes values hands them out, the later ones blend
     mixes = [dict(L.parts)["mixer"].get("value_mix") for L in spec.layers]
     assert mixes == [None, "source", None, "blend", "blend"]

@@ -44,6 +44,7 @@ def build_spec(cfg: BizepelConfig, max_positions: int | None = None) -> ModelSpe
     layers, runs = [], []
     renames = [("embed.weight", "embed"), ("embed.norm.weight", "embed.norm"), ("final.norm.weight", "final.norm")]
     mixes_values = False
+    optional = []
     n_layers = len(cfg.layers)
     for i, L in enumerate(cfg.layers):
         m, pre = L.mixer, f"l{i}."
@@ -59,6 +60,8 @@ def build_spec(cfg: BizepelConfig, max_positions: int | None = None) -> ModelSpe
                          position=position, window=m.window, keep_first=m.keep_first if m.window is not None else 0,
                          scale=m.scale, v_head_dim=m.vdim, in_bias=True, conv=m.conv, value_mix=mix)
             names = _ATTENTION_NAMES
+            if mix is None:
+                optional.append(f"{pre}mix.vmix")            # a file may carry the number for a layer that blends nothing
         elif L.kind == MAMBA1:
             mixer = part("selective_scan", width=W, inner=m.inner, state=m.state, dt_rank=m.dt_rank, conv=m.conv)
             names = _MAMBA_NAMES
@@ -95,6 +98,7 @@ def build_spec(cfg: BizepelConfig, max_positions: int | None = None) -> ModelSpe
             kind = "pre_norm_filtered"
         else:
             kind = "pre_norm_filtered_mixer_only"
+            optional += [f"{pre}norm2", f"{pre}canon2", f"{pre}ls2"]      # a file may carry them for a layer without feed-forward
         roles["tail"] = tail
         layers.append(layer(part(kind), prefix=pre, names=tuple((r, _NAMES[r]) for r in roles), **roles))
         runs.append(Run(i))
@@ -104,7 +108,7 @@ def build_spec(cfg: BizepelConfig, max_positions: int | None = None) -> ModelSpe
         layers=tuple(layers), runs=tuple(runs),
         final_norm=part("layer", width=W, eps=eps, scale=cfg.logit_scale), final_norm_name="final.norm.",
         head=part("linear", vocab_size=cfg.vocab, width=W, tied=True), head_name="head.",
-        stop_token_ids=tuple(cfg.eos_token_id), renames=tuple(renames))
+        stop_token_ids=tuple(cfg.eos_token_id), renames=tuple(renames), optional_tensors=tuple(optional))
 
 
 register_architecture(ArchitectureEntry(

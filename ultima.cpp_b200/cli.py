@@ -59,7 +59,7 @@ def cmd_archinfo(argv) -> int:
     from .weights import WeightError, check_weights
     if os.path.isfile(os.path.join(argv[0], "model.safetensors")) or \
             os.path.isfile(os.path.join(argv[0], "model.safetensors.index.json")):
-        optional = ("lm_head.weight",) if spec.head.get("tied") else ()
+        optional = (("lm_head.weight",) if spec.head.get("tied") else ()) + tuple(spec.optional_tensors)
         try:
             found = check_weights(argv[0], spec.weight_specs(), optional)
             kinds = sorted({dt for dt, _ in found.values()})
@@ -79,7 +79,7 @@ def _runnable(model_dir: str):
     try:
         cfg = config_from_dir(model_dir)
         spec = model_spec_for(cfg)
-        optional = ("lm_head.weight",) if spec.head.get("tied") else ()
+        optional = (("lm_head.weight",) if spec.head.get("tied") else ()) + tuple(spec.optional_tensors)
         found = check_weights(model_dir, spec.weight_specs(), optional)
     except (ConfigError, WeightError, SafetensorsError, OSError, ValueError) as e:
         return False, str(e).splitlines()[0] if str(e) else type(e).__name__

@@ -102,7 +102,7 @@ class Engine:
                     -(-int(kw.get("max_tokens", 4096)) // PAGE) * PAGE)
         spec = entry.build_spec(cfg, max_positions=reach)
         device = kw.get("device", "cuda:0")
-        optional = ("lm_head.weight",) if spec.head.get("tied") else ()
+        optional = (("lm_head.weight",) if spec.head.get("tied") else ()) + tuple(spec.optional_tensors)
         tensors = load_weights(model_dir, spec.weight_specs(), _dtype_of(dtype), device, optional)
         eng = cls(spec, tensors, dtype=dtype, **kw)
         eng.config = cfg

@@ -323,6 +323,9 @@ class ModelSpec:
     # > 0: the residual stream is kept in this many copies [streams, T, width], all equal to the embedding's output at
     # the start and summed before the final norm; the layers' arrangements then take the copies (family "connection")
     streams: int = 0
+    # stored names that a file may hold although the model has no use for them; they are then passed over (the norm of a
+    # feed-forward that a layer does not have, say)
+    optional_tensors: tuple = ()
 
     def stored_name(self, name: str) -> str:
         """The name under which the file holds the tensor a part calls ``name`` (prefix included)."""
