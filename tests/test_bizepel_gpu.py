@@ -101,16 +101,19 @@ def test_layer_norm_and_the_join_that_writes_the_next_norm(T, width, out_dtype):
             assert rel_err(o, ref) < tol, mode
 
 
+@pytest.mark.parametrize("long", [False, True])
 @pytest.mark.parametrize("taps", [1, 2, 3, 4, 7])
 @pytest.mark.parametrize("C", [5, 64, 300])
-def test_the_causal_convolution_over_portions_with_its_state(taps, C):
+def test_the_causal_convolution_over_portions_with_its_state(taps, C, long):
     """Two sequences of unequal lengths in slots 3 and 1, cut into portions down to one token: the inputs of before a
     portion come from the state, zeros before the start; with a bias on the inputs, with the input added, with a bias
-    of its own and SiLU, from a projection in K slices and from a column range of a wider row."""
+    of its own and SiLU, from a projection in K slices and from a column range of a wider row.  ``long``: portions of a
+    hundred tokens and more, which take the kernels that walk tokens (a channel, or four neighbouring ones, a thread)."""
     import plain_bizepel as P
     ops = _ops()
     g = torch.Generator().manual_seed(taps * 100 + C)
-    lens = [23, 9]
+    lens = [150, 90] if long else [23, 9]
+    cuts = ([100, 64], [1, 1], [49, 25]) if long else ([4, 1], [1, 1], [2, 2], [10, 5], [6, 0])
     u = [torch.randn(n, C, generator=g) for n in lens]
     w = torch.randn(C, taps, generator=g)
     bias, ob = torch.randn(C, generator=g), torch.randn(C, generator=g)
@@ -129,15 +132,16 @@ def test_the_causal_convolution_over_portions_with_its_state(taps, C):
         state = state[:, :taps - 1].contiguous() if taps > 1 else None
         at = [0, 0]
         got = [[], []]
-        for cut in ([4, 1], [1, 1], [2, 2], [10, 5], [6, 0]):
+        for cut in cuts:
             live = [i for i in (0, 1) if cut[i] > 0]
             b = _Batch([cut[i] for i in live], [[3, 1][i] for i in live])
             x = torch.cat([u[i][at[i]:at[i] + cut[i]] for i in live])
             off = 0
-            if variant == "slices":                                # the sum of three slices, in columns 7.. of a wider row
-                parts = torch.randn(3, x.shape[0], C + 11, generator=g)
-                parts[2, :, 7:7 + C] = x - parts[0, :, 7:7 + C] - parts[1, :, 7:7 + C]
-                x, off = parts, 7
+            if variant == "slices":                                # the sum of three slices, in columns 7.. (or 8..) of a wider row
+                off = 8 if long and C % 4 == 0 else 7
+                parts = torch.randn(3, x.shape[0], C + 12, generator=g)
+                parts[2, :, off:off + C] = x - parts[0, :, off:off + C] - parts[1, :, off:off + C]
+                x = parts
             xd = x.to(DEV)
             out = torch.empty(b.n_tokens, C, device=DEV)
             kw = {"bias": bias.to(DEV)} if variant == "input_bias" else {}

@@ -40,17 +40,70 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TO>((xr[i] - mean) * inv * w[i]);
 }
 
+// The same with a row held in registers: four neighbouring columns a load, one pass over global memory (rows of a
+// multiple of 4 columns, up to 256 * 4 * NCH of them).
+template <typename TO, int NCH>
+__global__ void __launch_bounds__(256)
+layernorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                     const int* __restrict__ rows, int width, float eps) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const long long r = rows ? rows[blockIdx.x] : blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + r * width);
+    const int chunks = width >> 2;
+    float4 v[NCH];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        const int c = threadIdx.x + i * 256;
+        v[i] = c < chunks ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = block_sum(s, red) / (float)width;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        if (threadIdx.x + i * 256 < chunks) {
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        }
+    }
+    const float inv = inv_rms(block_sum(ss, red), (float)width, eps);
+    TO* o = out + (long long)blockIdx.x * width;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < chunks) {
+            const float4 ww = w4[c];
+            const float y[4] = {v[i].x * inv * ww.x, v[i].y * inv * ww.y, v[i].z * inv * ww.z, v[i].w * inv * ww.w};
+            store_vec<TO, 4>(o + 4 * c, y);
+        }
+    }
+}
+
 UB_API int ub_layernorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int n_rows, int width,
                         float eps, cudaStream_t st) {
     if (n_rows <= 0) return 0;
     if (width <= 0) return UB_ERR_ARG;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (out_dtype != UB_F32 && out_dtype != UB_BF16) return UB_ERR_UNSUPPORTED;
     cudaError_t e;
+    const bool aligned = (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    if (width % 4 == 0 && width <= 256 * 4 * 8 && aligned) {
+        const int nch = (width / 4 + 255) / 256;
+#define GO(NCH) e = out_dtype == UB_F32 \
+            ? ub_launch_dependent(layernorm_vec_kernel<float, NCH>, dim3(n_rows), dim3(256), 0, st, x, w, (float*)out, rows, width, eps) \
+            : ub_launch_dependent(layernorm_vec_kernel<__nv_bfloat16, NCH>, dim3(n_rows), dim3(256), 0, st, x, w, (__nv_bfloat16*)out, rows, width, eps)
+        if (nch <= 1) GO(1); else if (nch <= 2) GO(2); else if (nch <= 4) GO(4); else GO(8);
+#undef GO
+        return (int)e;
+    }
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (out_dtype == UB_F32)
         e = ub_launch_dependent(layernorm_kernel<float>, dim3(n_rows), dim3(threads), 0, st, x, w, (float*)out, rows, width, eps);
-    else if (out_dtype == UB_BF16)
+    else
         e = ub_launch_dependent(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, st, x, w, (__nv_bfloat16*)out, rows, width, eps);
-    else return UB_ERR_UNSUPPORTED;
     return (int)e;
 }
 
@@ -226,6 +279,100 @@ causal_conv_tile_kernel(ConvIn in, const float* __restrict__ w, float* __restric
     }
 }
 
+// The tile walk with four neighbouring channels a thread (16-byte loads of float32, 8-byte loads of bfloat16): rows, column
+// ranges and the state on 16-byte boundaries, channels a multiple of 4.
+template <typename TX>
+__device__ __forceinline__ float4 conv_input4(const ConvIn& in, long long t, int c) {
+    const TX* x = (const TX*)in.x;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < in.n_parts; ++p) {
+        float a[4];
+        load_vec<TX, 4>(x + p * in.part_stride + t * in.ldx + in.col_off + c, a);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] += a[e];
+    }
+    if (in.bias) {
+        const float4 b = *reinterpret_cast<const float4*>(in.bias + c);
+        v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+    }
+    return make_float4(v[0], v[1], v[2], v[3]);
+}
+
+__device__ __forceinline__ void fma4(float4& acc, const float* w, const float4& x) {
+    acc.x = fmaf(w[0], x.x, acc.x); acc.y = fmaf(w[1], x.y, acc.y); acc.z = fmaf(w[2], x.z, acc.z); acc.w = fmaf(w[3], x.w, acc.w);
+}
+
+template <typename TX, typename TO, int K>
+__global__ void __launch_bounds__(128)
+causal_conv_vec4_kernel(ConvIn in, const float* __restrict__ w, const float* __restrict__ state,
+                        const int* __restrict__ tok_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                        TO* __restrict__ out, long long ldo, int n_tokens, int C, int add_input, int act, int mix_mode, int mix_lo,
+                        int mix_hi, const float* __restrict__ lam, float* __restrict__ shared, const float* __restrict__ out_bias) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= C) return;
+    float wt[K + 1][4];
+#pragma unroll
+    for (int j = 0; j <= K; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wt[j][e] = w[(long long)(c + e) * (K + 1) + j];
+    float4 win[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) win[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 ob = out_bias ? *reinterpret_cast<const float4*>(out_bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool mixes = mix_mode && c >= mix_lo && c < mix_hi;
+    const float l = (mixes && mix_mode == 2) ? *lam : 0.f;
+    const long long tbase = (long long)blockIdx.x * CONV_TILE;
+    const int seq0 = tok_seq[tbase];
+    const bool one_seq = tok_seq[min(tbase + CONV_TILE - 1, (long long)n_tokens - 1)] == seq0;
+    const int r0 = (int)tbase - seq_start[seq0];
+    float4 u_next = conv_input4<TX>(in, tbase, c);
+    for (int i = 0; i < CONV_TILE; ++i) {
+        const long long t = tbase + i;
+        if (t >= n_tokens) break;
+        const float4 u = u_next;
+        if (i + 1 < CONV_TILE && t + 1 < n_tokens) u_next = conv_input4<TX>(in, t + 1, c);
+        const int seq = one_seq ? seq0 : tok_seq[t];
+        const int r = one_seq ? r0 + i : (int)t - seq_start[seq];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i >= K && r >= K) {
+#pragma unroll
+            for (int j = K; j >= 1; --j) fma4(acc, wt[K - j], win[j - 1]);
+        } else {
+            const float* st = state + (long long)seq_slot[seq] * K * C;
+#pragma unroll
+            for (int j = K; j >= 1; --j) {
+                const float4 xv = (r - j >= 0) ? conv_input4<TX>(in, t - j, c)
+                                               : *reinterpret_cast<const float4*>(st + (long long)(K + r - j) * C + c);
+                fma4(acc, wt[K - j], xv);
+            }
+        }
+        fma4(acc, wt[K], u);
+        float y[4] = {acc.x, acc.y, acc.z, acc.w};
+        const float uu[4] = {u.x, u.y, u.z, u.w}, obv[4] = {ob.x, ob.y, ob.z, ob.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (add_input) y[e] += uu[e];
+            y[e] += obv[e];
+            if (act == 1) y[e] *= rw_sigmoid(y[e]);
+        }
+        if (mixes) {
+            float4* sh = reinterpret_cast<float4*>(shared + t * (mix_hi - mix_lo) + (c - mix_lo));
+            if (mix_mode == 1) *sh = make_float4(y[0], y[1], y[2], y[3]);
+            else {
+                const float4 o = *sh;
+                y[0] = (1.0f - l) * y[0] + l * o.x; y[1] = (1.0f - l) * y[1] + l * o.y;
+                y[2] = (1.0f - l) * y[2] + l * o.z; y[3] = (1.0f - l) * y[3] + l * o.w;
+            }
+        }
+        store_vec<TO, 4>(out + t * ldo + c, y);
+#pragma unroll
+        for (int j = K - 1; j >= 1; --j) win[j] = win[j - 1];
+        win[0] = u;
+    }
+}
+
 // One thread a (sequence, channel).
 template <typename TX>
 __global__ void causal_conv_state_kernel(ConvIn in, float* __restrict__ state, const int* __restrict__ seq_start,
@@ -263,8 +410,19 @@ UB_API int ub_causal_conv(const void* x, int x_dtype, long long ldx, int n_parts
     cudaError_t e;
 #define ARGS(TO) in, w, state, update_state, tok_seq, seq_start, seq_slot, (TO*)out, ldo, n_tokens, C
 #define TAIL add_input, act, mix_mode, mix_lo, mix_hi, lam, shared, out_bias
+    // four channels a thread where everything lies on 16-byte boundaries
+    const size_t xe = x_dtype == UB_F32 ? 4 : 2, oe = out_dtype == UB_F32 ? 4 : 2;
+    const bool vec4 = tiled && taps >= 2 && taps <= 4 && C % 4 == 0 && col_off % 4 == 0 && ldx % 4 == 0 && part_stride % 4 == 0 &&
+        ldo % 4 == 0 && ((uintptr_t)x % (4 * xe)) == 0 && ((uintptr_t)out % (4 * oe)) == 0 &&
+        (((uintptr_t)bias | (uintptr_t)out_bias | (uintptr_t)state | (uintptr_t)shared) & 15) == 0 &&
+        (!mix_mode || (mix_lo % 4 == 0 && mix_hi % 4 == 0));
+    const dim3 vgrid((n_tokens + CONV_TILE - 1) / CONV_TILE, (C / 4 + 127) / 128), vblock(128);
+#define VARGS(TO) in, w, (const float*)state, tok_seq, seq_start, seq_slot, (TO*)out, ldo, n_tokens, C
 #define GO(TX, TO) do { \
-        if (!tiled) e = ub_launch_dependent(causal_conv_kernel<TX, TO>, grid, block, 0, st, ARGS(TO), taps, TAIL); \
+        if (vec4 && taps == 2) e = ub_launch_dependent(causal_conv_vec4_kernel<TX, TO, 1>, vgrid, vblock, 0, st, VARGS(TO), TAIL); \
+        else if (vec4 && taps == 3) e = ub_launch_dependent(causal_conv_vec4_kernel<TX, TO, 2>, vgrid, vblock, 0, st, VARGS(TO), TAIL); \
+        else if (vec4) e = ub_launch_dependent(causal_conv_vec4_kernel<TX, TO, 3>, vgrid, vblock, 0, st, VARGS(TO), TAIL); \
+        else if (!tiled) e = ub_launch_dependent(causal_conv_kernel<TX, TO>, grid, block, 0, st, ARGS(TO), taps, TAIL); \
         else if (taps == 2) e = ub_launch_dependent(causal_conv_tile_kernel<TX, TO, 1>, tgrid, block, 0, st, ARGS(TO), TAIL); \
         else if (taps == 3) e = ub_launch_dependent(causal_conv_tile_kernel<TX, TO, 2>, tgrid, block, 0, st, ARGS(TO), TAIL); \
         else if (taps == 4) e = ub_launch_dependent(causal_conv_tile_kernel<TX, TO, 3>, tgrid, block, 0, st, ARGS(TO), TAIL); \
@@ -275,6 +433,7 @@ UB_API int ub_causal_conv(const void* x, int x_dtype, long long ldx, int n_parts
     else return UB_ERR_UNSUPPORTED;
 #undef GO
 #undef ARGS
+#undef VARGS
 #undef TAIL
     return (int)e;
 }
